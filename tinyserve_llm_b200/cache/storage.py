@@ -49,7 +49,7 @@ class DeviceCacheStorage:
         for group, pages in zip(layout.groups, counts):
             shape = (pages, len(group.entries), group.num_kv_heads, layout.page_tokens, group.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device) if group.values else None)
         self.state = None
         if layout.state_bytes:
             self.state = torch.zeros((max(num_state_slots, 1), layout.state_bytes), dtype=torch.uint8, device=self.device)
@@ -57,7 +57,7 @@ class DeviceCacheStorage:
     @staticmethod
     def bytes_per_page(layout: CacheLayout, dtype: torch.dtype) -> list[int]:
         """Keys and values of one page across the entries of each group."""
-        return [2 * len(g.entries) * g.num_kv_heads * layout.page_tokens * g.head_dim * dtype.itemsize
+        return [(2 if g.values else 1) * len(g.entries) * g.num_kv_heads * layout.page_tokens * g.head_dim * dtype.itemsize
                 for g in layout.groups]
 
     def entry_binding(self, entry: int) -> EntryBinding | None:

@@ -2,7 +2,7 @@
 Trace replay: feeds given token ids through a model step by step and writes the logits.
 
     bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
-                  [--page-tokens 64] [--caching off|on]
+                  [--page-tokens 64] [--max-requests 4] [--caching off|on]
 
 Steps come on standard input, one JSON object a line:
 
@@ -44,6 +44,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time, each rounded up to a multiple of the page size")
     parser.add_argument("--page-tokens", type=int, default=64, help="tokens per cache page (default 64)")
+    parser.add_argument("--max-requests", type=int, default=4,
+                        help="most requests live at any time: the state slots of models that keep per-request state (default 4)")
     parser.add_argument("--caching", choices=["on", "off"], default="off",
                         help="on: ended requests' pages stay indexed and new requests reuse them")
     args = parser.parse_args(argv)
@@ -59,7 +61,7 @@ def main(argv: list[str] | None = None) -> int:
     model = load_model(args.model, args.dtype, "cuda")
     num_pages = max(1, -(-args.max_tokens // args.page_tokens))
     _, manager, storage = build_cache(model, args.page_tokens, num_pages, caching=args.caching == "on",
-                                      num_state_slots=8)
+                                      num_state_slots=max(1, args.max_requests))
     runner = StepRunner(model, manager, storage)
     reused_tokens = 0
 

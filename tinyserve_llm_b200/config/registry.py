@@ -1,6 +1,6 @@
 """
-One registry from an architecture's name (config.json `architectures[0]`, with `model_type` as
-fallback) to its typed configuration and to the builder of its `ModelSpec`.
+One registry from an architecture's name (config.json `architectures[0]` or `architecture`, with
+`model_type` as fallback) to its typed configuration and to the builder of its `ModelSpec`.
 
 Reference behaviour: a dict from `model_type` to the model class, and NotImplementedError naming
 what is available for anything else (model/loader.py:22-25, :85-86).
@@ -13,6 +13,7 @@ import os
 from dataclasses import dataclass
 from typing import Any, Callable, Mapping
 
+from tinyserve_llm_b200.config.duduvik import DuduvikConfig, duduvik_model_spec
 from tinyserve_llm_b200.config.llama import ConfigError, LlamaConfig, llama_model_spec
 from tinyserve_llm_b200.config.spec import ModelSpec
 
@@ -34,10 +35,13 @@ def register_architecture(arch: Architecture) -> Architecture:
 
 
 register_architecture(Architecture("LlamaForCausalLM", "llama", LlamaConfig.from_dict, llama_model_spec))
+register_architecture(Architecture("Duduvik", "duduvik", DuduvikConfig.from_dict, duduvik_model_spec))
 
 
 def resolve_architecture(raw: Mapping[str, Any]) -> Architecture:
-    names = raw.get("architectures") or []
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):          # some configurations name their one architecture so
+        names.append(raw["architecture"])
     for name in names:
         if name in ARCHITECTURES:
             return ARCHITECTURES[name]

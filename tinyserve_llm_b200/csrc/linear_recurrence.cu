@@ -1,0 +1,224 @@
+// Linear attention as a recurrence with a decayed matrix state per request and head:
+//
+//   S_t = diag(a_t) S_(t-1) + k_t v_t^T        S: [key channels, value channels], float32
+//   o_t = S_t^T q_t
+//
+// with a_t either one constant per head (retention) or one value per key channel computed from a
+// projection's output z:  a = sigmoid(z + bias)^(1/tau), taken as exp(log_sigmoid(z + bias) / tau)
+// (gated linear attention).  q and k may be rotated (rotate-half over the first `rot_dims` channels
+// of a head, angle = position * freq[i]) and scaled on their way in.  Everything from the loaded
+// projections on is float32: rotation, decays, the state, the sums.
+//
+// One kernel serves prompts, portions of prompts and single decoded tokens: a CTA owns one request,
+// one head and 32 value channels, reads the state from the request's slot, walks over the request's
+// tokens of this step in order and writes the state back.  The arithmetic of a token does not depend
+// on where the step was cut or on what else is in the batch.  Tokens are staged 16 at a time
+// (rotation and decays computed by all threads in parallel); inside a tile no thread waits for
+// another: thread (r, j) holds rows r, r + 8, ... of column j of S and leaves its share of o_t[j] in
+// shared memory, and the eight shares are added up in a fixed order after the tile.
+//
+// A second kernel norms each head's o over the value channels (with or without a weight),
+// multiplies by silu(gate) and rounds to the activation dtype for the output projection.
+#include "common.cuh"
+
+constexpr int LR_ROWGROUPS = 8;     // warps of a CTA: warp r holds rows r, r + 8, ... of the state
+constexpr int LR_COLS = 32;         // value channels of a CTA
+constexpr int LR_TILE = 16;         // tokens staged at a time
+
+struct RecurrenceArgs {
+    const void* q; const void* k; const void* v;      // activation dtype, rows of the step's tokens
+    long long q_stride, k_stride, v_stride;           // elements between tokens
+    const float* z; long long z_stride;               // decay logits [tokens, heads * dim] (mode 1)
+    const float* bias;                                // [heads * dim] added to z (mode 1), may be null
+    const float* head_decay;                          // [heads] (mode 0)
+    float inv_tau;
+    float q_scale, k_scale;
+    const float* freq; int rot_dims;                  // rotation of q and k (freq null: none)
+    const int* positions;
+    const int* cu_q; const int* slots;
+    float* state; long long slot_stride;              // floats between slots; a slot holds [heads, dim, vdim]
+    float* out;                                       // [tokens, heads * vdim] float32
+    int heads, dim, vdim;
+};
+
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+template <typename T, int MAXM>
+__global__ void __launch_bounds__(LR_ROWGROUPS * LR_COLS)
+linear_recurrence_kernel(RecurrenceArgs p) {
+    extern __shared__ float smem[];
+    const int dim = p.dim, vdim = p.vdim;
+    float* q_s = smem;                                   // [LR_TILE][dim]
+    float* k_s = q_s + LR_TILE * dim;                    // [LR_TILE][dim]
+    float* a_s = k_s + LR_TILE * dim;                    // [LR_TILE][dim]
+    float* v_s = a_s + LR_TILE * dim;                    // [LR_TILE][LR_COLS]
+    float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
+    const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
+    const int slot = p.slots[seq];
+    const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
+    if (slot < 0 || end <= begin) return;                // a padding request, or one that feeds nothing
+    const int r = threadIdx.x / LR_COLS, jj = threadIdx.x % LR_COLS, j = j0 + jj;
+    const bool live = j < vdim;
+    float* st = p.state + (long long)slot * p.slot_stride + (long long)h * dim * vdim;
+    float S[MAXM];
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+        const int i = r + LR_ROWGROUPS * m;
+        S[m] = (live && i < dim) ? st[(long long)i * vdim + j] : 0.f;
+    }
+    const T* q = (const T*)p.q;
+    const T* k = (const T*)p.k;
+    const T* v = (const T*)p.v;
+    const int half = p.rot_dims / 2;
+    const float head_decay = p.head_decay ? p.head_decay[h] : 1.f;
+    for (int t0 = begin; t0 < end; t0 += LR_TILE) {
+        const int n = min(LR_TILE, end - t0);
+        __syncthreads();                                 // the tile before has been read
+        for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+            const int tt = e / dim, i = e % dim;
+            const long long t = t0 + tt;
+            const T* qr = q + t * p.q_stride + (long long)h * dim;
+            const T* kr = k + t * p.k_stride + (long long)h * dim;
+            float qv = to_float<T>(qr[i]), kv = to_float<T>(kr[i]);
+            if (p.freq && i < p.rot_dims) {
+                const int f = i < half ? i : i - half;
+                const float angle = (float)p.positions[t] * p.freq[f];
+                float sn, cs;
+                sincosf(angle, &sn, &cs);
+                const int other = i < half ? i + half : i - half;
+                const float qo = to_float<T>(qr[other]), ko = to_float<T>(kr[other]);
+                // first half: u cos - v sin; second half: v cos + u sin
+                qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
+                kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+            }
+            q_s[e] = qv * p.q_scale;
+            k_s[e] = kv * p.k_scale;
+            float a = head_decay;
+            if (p.z) {
+                float x = p.z[t * p.z_stride + (long long)h * dim + i];
+                if (p.bias) x += p.bias[h * dim + i];
+                a = expf(log_sigmoid(x) * p.inv_tau);
+            }
+            a_s[e] = a;
+        }
+        for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
+            const int tt = e / LR_COLS, c = e % LR_COLS;
+            v_s[e] = (j0 + c < vdim) ? to_float<T>(v[(long long)(t0 + tt) * p.v_stride + (long long)h * vdim + j0 + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = v_s[tt * LR_COLS + jj];
+            const float* qt = q_s + tt * dim;
+            const float* kt = k_s + tt * dim;
+            const float* at = a_s + tt * dim;
+            float acc = 0.f;
+#pragma unroll
+            for (int m = 0; m < MAXM; ++m) {
+                const int i = r + LR_ROWGROUPS * m;
+                if (i < dim) {
+                    S[m] = fmaf(at[i], S[m], kt[i] * vj);
+                    acc = fmaf(S[m], qt[i], acc);
+                }
+            }
+            part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
+            const int tt = e / LR_COLS, c = e % LR_COLS;
+            if (j0 + c >= vdim) continue;
+            float o = 0.f;
+#pragma unroll
+            for (int g = 0; g < LR_ROWGROUPS; ++g) o += part[(tt * LR_ROWGROUPS + g) * LR_COLS + c];
+            p.out[(long long)(t0 + tt) * p.heads * vdim + (long long)h * vdim + j0 + c] = o;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+        const int i = r + LR_ROWGROUPS * m;
+        if (live && i < dim) st[(long long)i * vdim + j] = S[m];
+    }
+}
+
+template <typename T>
+static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t stream) {
+    dim3 grid((p.vdim + LR_COLS - 1) / LR_COLS, p.heads, num_seqs);
+    const size_t smem = (size_t)(3 * LR_TILE * p.dim + LR_TILE * LR_COLS + LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);
+#define TS_RECURRENCE(MAXM)                                                                                        \
+    do {                                                                                                           \
+        if (smem > 48 * 1024)                                                                                      \
+            cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                 (int)smem);                                                                       \
+        linear_recurrence_kernel<T, MAXM><<<grid, LR_ROWGROUPS * LR_COLS, smem, stream>>>(p);                      \
+    } while (0)
+    if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4);
+    else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8);
+    else if (p.dim <= 16 * LR_ROWGROUPS) TS_RECURRENCE(16);
+    else TS_RECURRENCE(32);
+#undef TS_RECURRENCE
+    TS_LAUNCH_CHECK("linear_recurrence");
+    return 0;
+}
+
+TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                long long v_stride, const float* z, long long z_stride, const float* bias,
+                                const float* head_decay, float inv_tau, float q_scale, float k_scale, const float* freq,
+                                int rot_dims, const int* positions, const int* cu_q, const int* slots, int num_seqs,
+                                float* state, long long slot_stride, float* out, int heads, int dim, int vdim,
+                                int dtype, cudaStream_t stream) {
+    TS_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && num_seqs >= 0, "linear_recurrence: bad sizes");
+    TS_REQUIRE(dim <= 32 * LR_ROWGROUPS, "linear_recurrence: %d key channels a head are not supported (up to %d)", dim,
+               32 * LR_ROWGROUPS);
+    TS_REQUIRE(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0, "linear_recurrence: rotation over %d of %d channels",
+               rot_dims, dim);
+    TS_REQUIRE((z != nullptr) != (head_decay != nullptr), "linear_recurrence: either decay logits or one decay per head");
+    TS_REQUIRE(slot_stride >= (long long)heads * dim * vdim, "linear_recurrence: a state slot is too small");
+    TS_REQUIRE(num_seqs <= 65535 && heads <= 65535, "linear_recurrence: grid too large");
+    if (num_seqs == 0) return 0;
+    RecurrenceArgs p{q, k, v, q_stride, k_stride, v_stride, z, z_stride, bias, head_decay, inv_tau, q_scale, k_scale,
+                     rot_dims > 0 ? freq : nullptr, rot_dims, positions, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
+    if (dtype == TS_F32) return launch_recurrence<float>(p, num_seqs, stream);
+    if (dtype == TS_BF16) return launch_recurrence<__nv_bfloat16>(p, num_seqs, stream);
+    return ts_fail("linear_recurrence: unknown dtype code %d", dtype);
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); one warp a (token, head).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
+                                      const float* __restrict__ weight, T* __restrict__ out, long long items, int heads,
+                                      int vdim, float eps) {
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = item / heads;
+    const int h = (int)(item % heads);
+    const float* orow = o + item * vdim;
+    float acc = 0.f;
+    for (int j = lane; j < vdim; j += 32) acc += orow[j] * orow[j];
+    const float inv = 1.f / sqrtf(warp_sum(acc) / (float)vdim + eps);
+    const T* g = gate + t * gate_stride + (long long)h * vdim;
+    T* dst = out + item * vdim;
+    for (int j = lane; j < vdim; j += 32) {
+        const float x = to_float<T>(g[j]);
+        const float silu = x / (1.f + expf(-x));
+        const float w = weight ? weight[j] : 1.f;
+        dst[j] = from_float<T>(orow[j] * inv * w * silu);
+    }
+}
+
+TS_API int ts_head_norm_gate(const float* o, const void* gate, long long gate_stride, const float* weight, void* out,
+                             int num_tokens, int heads, int vdim, float eps, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && heads > 0 && vdim > 0, "head_norm_gate: bad sizes");
+    if (num_tokens == 0) return 0;
+    const long long items = (long long)num_tokens * heads;
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    if (dtype == TS_F32)
+        head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, gate_stride, weight, (float*)out,
+                                                                 items, heads, vdim, eps);
+    else if (dtype == TS_BF16)
+        head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, gate_stride, weight,
+                                                                         (__nv_bfloat16*)out, items, heads, vdim, eps);
+    else
+        return ts_fail("head_norm_gate: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("head_norm_gate");
+    return 0;
+}

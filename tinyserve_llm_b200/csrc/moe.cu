@@ -1,0 +1,287 @@
+// Routed experts: every token goes through its `top` best experts of `experts` small gated
+// feed-forward layers, and the outputs are added with the softmax of the chosen logits as weights.
+//
+//   ts_moe_route     per token: the `top` largest router logits (float32, bias added here; ties go to
+//                    the lower index), their softmax, and a count per expert.
+//   ts_moe_arrange   (token, choice) pairs sorted by expert: every CTA takes the exclusive scan of the
+//                    counts and places its pairs behind their expert's offset.  Which row of an
+//                    expert's stretch a pair lands in is not fixed; no result depends on it.
+//   ts_moe_linear    grouped product over the sorted pairs: row i of expert e's stretch times W_e^T,
+//                    W [experts, N, K].  Tiles of 32 pairs x 64 columns, FFMA with float32 sums over k
+//                    in ascending order (a pair's result does not depend on its row or on the batch).
+//                    With `gated`, W_e holds gate rows then up rows and the epilogue applies the gated
+//                    activation (see activation.cu for the kinds) before it stores.  Input rows are
+//                    gathered by token for the first product; the second reads the sorted rows.
+//   ts_moe_combine   out[t] = sum_j share[t, j] * y[row of (t, j)] (+ the shared expert's output), in the
+//                    order of j, float32, rounded once.
+#include "common.cuh"
+
+__device__ __forceinline__ float gated_activation(int kind, float g, float u, float limit, float alpha);
+
+// kind 0: silu(g) * u;  1: relu(g) * u;  2: g' * sigmoid(alpha g') * (u' + 1) with g' = min(g, limit),
+// u' = clamp(u, -limit, limit)
+__device__ __forceinline__ float gated_activation(int kind, float g, float u, float limit, float alpha) {
+    if (kind == 1) return fmaxf(g, 0.f) * u;
+    if (kind == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                 const int* __restrict__ seq_of_token, int* __restrict__ chosen, float* __restrict__ share,
+                                 int* __restrict__ counts, int num_tokens, int experts, int top) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= num_tokens) return;
+    const int lane = threadIdx.x & 31;
+    if (seq_of_token && seq_of_token[t] < 0) {            // a padding row takes part in nothing
+        for (int j = lane; j < top; j += 32) chosen[(long long)t * top + j] = -1;
+        return;
+    }
+    const float* z = logits + (long long)t * experts;
+    float first = 0.f, total = 0.f;
+    unsigned long long taken_lo = 0;                       // experts this lane has given away (its e = lane + 32 i, i < 64)
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane, i = 0; e < experts; e += 32, ++i) {
+            if (taken_lo >> i & 1) continue;
+            const float x = z[e] + (bias ? bias[e] : 0.f);
+            if (x > best || (x == best && e < arg)) { best = x; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (arg != 0x7fffffff && (arg & 31) == lane) taken_lo |= 1ull << (arg >> 5);
+        if (j == 0) first = best;
+        const float w = expf(best - first);                // the first choice is the largest
+        total += w;
+        if (lane == 0) {
+            chosen[(long long)t * top + j] = arg;
+            share[(long long)t * top + j] = w;
+            atomicAdd(counts + arg, 1);
+        }
+    }
+    __syncwarp();
+    if (lane == 0)
+        for (int j = 0; j < top; ++j) share[(long long)t * top + j] /= total;
+}
+
+TS_API int ts_moe_route(const float* logits, const float* bias, const int* seq_of_token, int* chosen, float* share,
+                        int* counts, int num_tokens, int experts, int top, cudaStream_t stream) {
+    TS_REQUIRE(experts > 0 && top > 0 && top <= experts, "moe_route: %d of %d experts", top, experts);
+    TS_REQUIRE(experts <= 2048, "moe_route: %d experts are not supported (up to 2048)", experts);
+    if (num_tokens <= 0) return 0;
+    moe_route_kernel<<<(num_tokens + 3) / 4, 128, 0, stream>>>(logits, bias, seq_of_token, chosen, share, counts,
+                                                               num_tokens, experts, top);
+    TS_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+// offsets[e] = pairs of experts before e (offsets[experts] = all); row_of_pair / pair_of_row both ways.
+__global__ void moe_arrange_kernel(const int* __restrict__ chosen, const int* __restrict__ counts, int* __restrict__ cursor,
+                                   int* __restrict__ offsets, int* __restrict__ pair_of_row, int* __restrict__ row_of_pair,
+                                   int pairs, int experts) {
+    extern __shared__ int start[];                        // experts + 1
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; ++e) { start[e] = run; run += counts[e]; }
+        start[experts] = run;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0)
+        for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
+        const int e = chosen[p];
+        if (e < 0) { row_of_pair[p] = -1; continue; }
+        const int row = start[e] + atomicAdd(cursor + e, 1);
+        pair_of_row[row] = p;
+        row_of_pair[p] = row;
+    }
+}
+
+TS_API int ts_moe_arrange(const int* chosen, const int* counts, int* cursor, int* offsets, int* pair_of_row,
+                          int* row_of_pair, int pairs, int experts, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    const int blocks = min((pairs + 255) / 256, 148);
+    moe_arrange_kernel<<<blocks, 256, (experts + 1) * sizeof(int), stream>>>(chosen, counts, cursor, offsets, pair_of_row,
+                                                                           row_of_pair, pairs, experts);
+    TS_LAUNCH_CHECK("moe_arrange");
+    return 0;
+}
+
+constexpr int GM = 32, GN = 64, GK = 16;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ pair_of_row, int top,
+                  const int* __restrict__ offsets, int experts, const T* __restrict__ w, int N, int K, T* __restrict__ y,
+                  int out_cols, int kind, float limit, float alpha) {
+    __shared__ float As[GK][GM + 1];
+    __shared__ float Bs[GK][GN + 1];
+    __shared__ float Us[GATED ? GK : 1][GN + 1];
+    __shared__ int rows_src[GM];
+    // which expert's stretch this row tile belongs to: tiles are numbered expert by expert
+    int tile = blockIdx.y, e = 0, first = 0, last = 0;
+    for (; e < experts; ++e) {
+        first = offsets[e]; last = offsets[e + 1];
+        const int tiles = (last - first + GM - 1) / GM;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (e == experts) return;
+    const int row0 = first + tile * GM;
+    const int nrows = min(GM, last - row0);
+    const int col0 = blockIdx.x * GN;
+    const int tid = threadIdx.x;
+    if (tid < GM) {
+        int src = -1;
+        if (tid < nrows) src = pair_of_row ? pair_of_row[row0 + tid] / top : row0 + tid;
+        rows_src[tid] = src;
+    }
+    __syncthreads();
+    const T* we = w + (long long)e * N * K;
+    const int half = GATED ? N / 2 : 0;                   // gate rows [0, half), up rows [half, N)
+    const int tr = (tid / 16) * 2, tc = (tid % 16) * 4;   // 2 x 4 outputs a thread
+    float acc[2][4], accu[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = accu[i][j] = 0.f;
+    const int lk = tid % GK, lr = tid / GK;               // 16 rows of loads a pass
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        const int gk = k0 + lk;
+#pragma unroll
+        for (int i = 0; i < GM / 16; ++i) {
+            const int r = lr + 16 * i;
+            const int src = rows_src[r];
+            As[lk][r] = (src >= 0 && gk < K) ? to_float<T>(x[(long long)src * x_stride + gk]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < GN / 16; ++i) {
+            const int c = lr + 16 * i;
+            const int gc = col0 + c;
+            const bool in = gc < (GATED ? half : N) && gk < K;
+            Bs[lk][c] = in ? to_float<T>(we[(long long)gc * K + gk]) : 0.f;
+            if (GATED) Us[lk][c] = in ? to_float<T>(we[(long long)(half + gc) * K + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GK; ++k) {
+            float a[2], b[4], u[4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) a[i] = As[k][tr + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { b[j] = Bs[k][tc + j]; if (GATED) u[j] = Us[k][tc + j]; }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if (GATED) accu[i][j] = fmaf(a[i], u[j], accu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (tr + i >= nrows) continue;
+        T* dst = y + (long long)(row0 + tr + i) * out_cols;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gc = col0 + tc + j;
+            if (gc >= out_cols) continue;
+            const float v = GATED ? gated_activation(kind, acc[i][j], accu[i][j], limit, alpha) : acc[i][j];
+            dst[gc] = from_float<T>(v);
+        }
+    }
+}
+
+TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_row, int top, const int* offsets,
+                         int experts, const void* w, int N, int K, void* y, int pairs, int gated, int kind, float limit,
+                         float alpha, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(experts > 0 && N > 0 && K > 0 && top > 0, "moe_linear: bad sizes");
+    TS_REQUIRE(!gated || N % 2 == 0, "moe_linear: a gated weight holds gate and up rows of equal number");
+    if (pairs <= 0) return 0;
+    const int out_cols = gated ? N / 2 : N;
+    const int row_tiles = (pairs + GM - 1) / GM + experts;       // every expert may end in a ragged tile
+    TS_REQUIRE(row_tiles <= 65535, "moe_linear: %d pairs need more than 65535 row tiles", pairs);
+    dim3 grid((out_cols + GN - 1) / GN, row_tiles);
+#define TS_MOE_LINEAR(TYPE, G)                                                                                       \
+    moe_linear_kernel<TYPE, G><<<grid, 256, 0, stream>>>((const TYPE*)x, x_stride, pair_of_row, top, offsets, experts, \
+                                                         (const TYPE*)w, N, K, (TYPE*)y, out_cols, kind, limit, alpha)
+    if (dtype == TS_F32) { if (gated) TS_MOE_LINEAR(float, true); else TS_MOE_LINEAR(float, false); }
+    else if (dtype == TS_BF16) { if (gated) TS_MOE_LINEAR(__nv_bfloat16, true); else TS_MOE_LINEAR(__nv_bfloat16, false); }
+    else return ts_fail("moe_linear: unknown dtype code %d", dtype);
+#undef TS_MOE_LINEAR
+    TS_LAUNCH_CHECK("moe_linear");
+    return 0;
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ share, const T* __restrict__ shared_out, T* __restrict__ out,
+                                   int width, int top) {
+    const long long t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int row = row_of_pair[t * top + j];
+            if (row >= 0) s = fmaf(share[t * top + j], to_float<T>(y[(long long)row * width + i]), s);
+        }
+        if (shared_out) s += to_float<T>(shared_out[t * width + i]);
+        out[t * width + i] = from_float<T>(s);
+    }
+}
+
+TS_API int ts_moe_combine(const void* y, const int* row_of_pair, const float* share, const void* shared_out, void* out,
+                          int num_tokens, int width, int top, int dtype, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (dtype == TS_F32)
+        moe_combine_kernel<float><<<num_tokens, 128, 0, stream>>>((const float*)y, row_of_pair, share,
+                                                                  (const float*)shared_out, (float*)out, width, top);
+    else if (dtype == TS_BF16)
+        moe_combine_kernel<__nv_bfloat16><<<num_tokens, 128, 0, stream>>>((const __nv_bfloat16*)y, row_of_pair, share,
+            (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, width, top);
+    else
+        return ts_fail("moe_combine: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("moe_combine");
+    return 0;
+}
+
+// out[t, i] = activation(gate_up[t, i], gate_up[t, I + i]) for the kinds above (dense layers and the shared expert).
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter,
+                                        int kind, float limit, float alpha) {
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / inter;
+        const int i = (int)(idx % inter);
+        const float g = to_float<T>(gate_up[t * 2 * inter + i]);
+        const float u = to_float<T>(gate_up[t * 2 * inter + inter + i]);
+        out[idx] = from_float<T>(gated_activation(kind, g, u, limit, alpha));
+    }
+}
+
+TS_API int ts_gated_activation(const void* gate_up, void* out, int num_tokens, int inter, int kind, float limit,
+                               float alpha, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && inter > 0 && kind >= 0 && kind <= 2, "gated_activation: bad arguments");
+    if (num_tokens == 0) return 0;
+    const long long total = (long long)num_tokens * inter;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == TS_F32)
+        gated_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter, kind,
+                                                                   limit, alpha);
+    else if (dtype == TS_BF16)
+        gated_activation_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
+                                                                           (__nv_bfloat16*)out, total, inter, kind, limit, alpha);
+    else
+        return ts_fail("gated_activation: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("gated_activation");
+    return 0;
+}

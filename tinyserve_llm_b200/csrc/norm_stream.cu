@@ -1,0 +1,82 @@
+// RMS norms around a residual stream that is kept in float32 whatever the activation dtype.
+//
+// One kernel does what lies between two sublayers of a block that norms each sublayer's input and
+// output:  s = stream + closing(branch),  stream' = s,  out = opening(s)  with
+//   closing(b) = b / sqrt(mean(b^2) + eps) * w_close      (the norm after the sublayer that made b)
+//   opening(s) = s / sqrt(mean(s^2) + eps) * w_open       (the norm before the next sublayer)
+// Every part is optional: no branch (the stream is only normed: a block's first norm after a block
+// that closed its own branch), no opening weight (the branch is only added), `rows` (only these
+// rows are normed into a compact output and the stream is not written: the final norm of the
+// wanted places), `ids` (the row is table[ids[r]] * scale and starts the stream: the embedding).
+// Statistics, weights, the sum and the stream are float32; the branch and `out` have the activation
+// dtype.  The weights are given as they multiply (an offset of the stored weight is added by the host).
+#include "common.cuh"
+
+template <typename T>
+__global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __restrict__ w_close, float* stream,
+                                   const float* __restrict__ w_open, T* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps, const T* __restrict__ table,
+                                   const int* __restrict__ ids, int table_rows, float scale, int write_stream) {
+    extern __shared__ float row[];                // width floats, then 32 of scratch
+    float* scratch = row + width;
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    if (src < 0) return;                          // a padding row
+    float* sr = stream + (long long)src * width;
+    if (ids) {
+        const int id = ids[src];
+        const bool zeros = id < 0 || id >= table_rows;
+        const T* tr = table + (long long)(zeros ? 0 : id) * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = zeros ? 0.f : to_float<T>(tr[i]) * scale;
+    } else if (branch) {
+        const T* br = branch + (long long)src * width;
+        float acc = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float b = to_float<T>(br[i]);
+            row[i] = b;
+            acc += b * b;
+        }
+        const float inv = 1.f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+        __syncthreads();                          // scratch is used again below
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = sr[i] + row[i] * inv * w_close[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = sr[i];
+    }
+    if (write_stream && (ids || branch))
+        for (int i = threadIdx.x; i < width; i += blockDim.x) sr[i] = row[i];
+    if (!w_open) return;
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) acc += row[i] * row[i];
+    const float inv = 1.f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
+    T* o = out + (long long)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(row[i] * inv * w_open[i]);
+}
+
+TS_API int ts_stream_norm(const void* branch, const float* w_close, float* stream, const float* w_open, void* out,
+                          const int* rows, int count, int width, float eps, const void* table, const int* ids,
+                          int table_rows, float scale, int dtype, cudaStream_t stream_handle) {
+    TS_REQUIRE(count >= 0 && width > 0, "stream_norm: bad sizes rows=%d width=%d", count, width);
+    TS_REQUIRE(stream != nullptr, "stream_norm: no residual stream");
+    TS_REQUIRE(!(branch && !w_close), "stream_norm: a branch needs the weight of its closing norm");
+    TS_REQUIRE(!(w_open && !out), "stream_norm: an opening norm needs an output");
+    TS_REQUIRE(!(ids && (!table || branch)), "stream_norm: token ids need the table and exclude a branch");
+    TS_REQUIRE(width <= 48 * 1024, "stream_norm: rows of %d elements are not supported", width);
+    if (count == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)(width + 32) * sizeof(float);
+    const int write = rows ? 0 : 1;
+#define TS_STREAM_NORM(TYPE)                                                                                      \
+    do {                                                                                                          \
+        if (smem > 48 * 1024)                                                                                     \
+            cudaFuncSetAttribute(stream_norm_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        stream_norm_kernel<TYPE><<<count, threads, smem, stream_handle>>>(                                        \
+            (const TYPE*)branch, w_close, stream, w_open, (TYPE*)out, rows, width, eps, (const TYPE*)table, ids,  \
+            table_rows, scale, write);                                                                            \
+    } while (0)
+    if (dtype == TS_F32) TS_STREAM_NORM(float);
+    else if (dtype == TS_BF16) TS_STREAM_NORM(__nv_bfloat16);
+    else return ts_fail("stream_norm: unknown dtype code %d", dtype);
+#undef TS_STREAM_NORM
+    TS_LAUNCH_CHECK("stream_norm");
+    return 0;
+}

@@ -24,7 +24,7 @@ TS_API int ts_copy_page_slots(void* k_pool, void* v_pool, int num_pages, int ent
     const long long run16 = (long long)page_tokens * hd * elem_bytes / 16;
     const long long page16 = run16 * entries * nkv;
     const long long copy16 = (long long)num_slots * hd * elem_bytes / 16;
-    dim3 grid(entries * nkv, 2);
+    dim3 grid(entries * nkv, v_pool ? 2 : 1);               // a group without a value pool copies its keys only
     copy_page_slots_kernel<<<grid, 128, 0, stream>>>((uint4*)k_pool, (uint4*)v_pool, page16, run16, entries * nkv,
                                                     src_page, dst_page, copy16);
     TS_LAUNCH_CHECK("copy_page_slots");

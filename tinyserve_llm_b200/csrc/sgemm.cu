@@ -2,13 +2,17 @@
 // engine's true 32-bit projection (no tensor-core mode that rounds its inputs).  Each output element
 // sums over k in ascending order, so a row's result does not depend on what else is in the batch.
 // Any M, N, K; rows of A and B are K-contiguous (the checkpoint's [out_features, in_features]).
+// A batched form runs one such product per blockIdx.z.
 #include "common.cuh"
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __global__ void __launch_bounds__(256)
 sgemm_nt_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
-                long long lda, long long ldb, long long ldc) {
+                long long lda, long long ldb, long long ldc, long long batch_a, long long batch_b, long long batch_c) {
+    A += blockIdx.z * batch_a;                            // one product per blockIdx.z (strides 0: a single product)
+    B += blockIdx.z * batch_b;
+    C += blockIdx.z * batch_c;
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -64,7 +68,22 @@ TS_API int ts_sgemm_nt(const float* A, const float* B, float* C, int M, int N, i
     if (M == 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     TS_REQUIRE(grid.y <= 65535, "sgemm: M=%d needs more than 65535 row tiles", M);
-    sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
+    sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, 0);
     TS_LAUNCH_CHECK("sgemm");
+    return 0;
+}
+
+// `batch` products at once: product b reads A + b * batch_a and B + b * batch_b and writes C + b * batch_c
+// (the per-head products of an attention that folds its key and value projections into query and output).
+TS_API int ts_sgemm_nt_batched(const float* A, const float* B, float* C, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, int batch, long long batch_a, long long batch_b,
+                               long long batch_c, cudaStream_t stream) {
+    TS_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0, "sgemm_batched: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    TS_REQUIRE(lda >= K && ldb >= K, "sgemm_batched: row strides smaller than the rows");
+    if (M == 0) return 0;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    TS_REQUIRE(grid.y <= 65535 && batch <= 65535, "sgemm_batched: grid too large");
+    sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, batch_a, batch_b, batch_c);
+    TS_LAUNCH_CHECK("sgemm_batched");
     return 0;
 }

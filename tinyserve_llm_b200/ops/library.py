@@ -48,6 +48,17 @@ _SIGNATURES = {
     "ts_skinny_linear_max_rows": ("int", ""),
     "ts_skinny_linear": ("int", "pppiiilliip"),
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
+    "ts_stream_norm": ("int", "ppppppiifppifip"),
+    "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiip"),
+    "ts_head_norm_gate": ("int", "pplppiiifip"),
+    "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
+    "ts_latent_attention": ("int", "pllpliipplliipipppiiiifiip"),
+    "ts_moe_route": ("int", "ppppppiiip"),
+    "ts_moe_arrange": ("int", "ppppppiip"),
+    "ts_moe_linear": ("int", "plpipipiipiiiffip"),
+    "ts_moe_combine": ("int", "pppppiiiip"),
+    "ts_gated_activation": ("int", "ppiiiffip"),
+    "ts_sgemm_nt_batched": ("int", "pppiiilllilllp"),
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 _RETURNS = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "void": None, "const char*": ctypes.c_char_p}
@@ -392,6 +403,222 @@ class Ops:
                    scale, window, _DTYPE_CODE[qkv.dtype], _stream())
         return out
 
+    # ------------------------------------------------------------------ float32 residual stream
+    def stream_norm(self, branch: torch.Tensor | None, w_close: torch.Tensor | None, stream: torch.Tensor,
+                    w_open: torch.Tensor | None, eps: float, dtype: torch.dtype, rows: torch.Tensor | None = None,
+                    table: torch.Tensor | None = None, ids: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor | None:
+        """
+        stream (float32, in place) += closing norm of `branch` (if given); returns the opening norm of
+        the sum in `dtype` (if `w_open` is given).  With `rows` only those rows are normed, into a
+        compact output, and the stream is left as it is.  With `table` and `ids` the rows
+        table[ids] * scale start the stream instead.  Weights are float32 and multiply as given.
+        """
+        self._check(stream, "residual stream", torch.float32, 2)
+        width = stream.shape[1]
+        for w, name in ((w_close, "closing weight"), (w_open, "opening weight")):
+            if w is not None:
+                self._check(w, name, torch.float32, 1)
+                if w.shape[0] != width:
+                    raise KernelError(f"{name} has {w.shape[0]} elements for rows of {width}")
+        if branch is not None:
+            self._check(branch, "branch", dtype, 2)
+            if branch.shape != stream.shape:
+                raise KernelError(f"branch {tuple(branch.shape)} does not match the stream {tuple(stream.shape)}")
+        if ids is not None:
+            self._check(table, "embedding table", dtype, 2)
+            self._check(ids, "token ids", torch.int32, 1)
+            if table.shape[1] != width or ids.shape[0] != stream.shape[0]:
+                raise KernelError("stream_norm: the table's rows or the number of ids do not match the stream")
+        count = stream.shape[0]
+        if rows is not None:
+            self._check(rows, "rows", torch.int32, 1)
+            count = rows.shape[0]
+        out = None
+        if w_open is not None:
+            out = torch.empty((count, width), dtype=dtype, device=stream.device)
+        self._call("ts_stream_norm", _ptr(branch), _ptr(w_close), _ptr(stream), _ptr(w_open), _ptr(out), _ptr(rows), count,
+                   width, eps, _ptr(table), _ptr(ids), table.shape[0] if table is not None else 0, scale,
+                   _DTYPE_CODE[dtype], _stream())
+        return out
+
+    # ------------------------------------------------------------------ linear recurrences
+    def linear_recurrence(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx, binding, *, heads: int, dim: int,
+                          vdim: int, z: torch.Tensor | None, bias: torch.Tensor | None, head_decays: torch.Tensor | None,
+                          inv_tau: float, q_scale: float, k_scale: float, position=None) -> torch.Tensor:
+        """
+        float32 [T, heads * vdim]: o_t = S_t^T q_t with S_t = diag(a_t) S_(t-1) + k_t v_t^T per request and
+        head, the state read from and written back to the request's slot (`binding.state`).  q, k, v are
+        column slices of one projection output (unit stride inside a row).  Decays: `z` (float32
+        [T, heads * dim] logits, a = sigmoid(z + bias)^inv_tau) or `head_decays` (float32 [heads]).
+        """
+        for t, name, cols in ((q, "q", heads * dim), (k, "k", heads * dim), (v, "v", heads * vdim)):
+            if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != cols or t.dtype not in _DTYPE_CODE:
+                raise KernelError(f"linear_recurrence: {name} must be a CUDA [T, {cols}] slice with unit column stride")
+        if binding is None or binding.state is None or binding.state_slots is None:
+            raise KernelError("linear_recurrence: the cache entry has no state slot")
+        state = binding.state
+        if state.stride(1) != 1 or state.stride(0) % 4 or state.data_ptr() % 4 or state.shape[1] < heads * dim * vdim * 4:
+            raise KernelError("linear_recurrence: the state rows are not float32-aligned or too small")
+        T = q.shape[0]
+        if z is not None:
+            self._check(z, "decay logits", torch.float32, 2)
+            if tuple(z.shape) != (T, heads * dim):
+                raise KernelError(f"linear_recurrence: decay logits are {tuple(z.shape)}, expected {(T, heads * dim)}")
+        freq, rot = None, 0
+        if position is not None:
+            freq, rot = position.frequencies, position.dims
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
+        self._call("ts_linear_recurrence", _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(z),
+                   z.stride(0) if z is not None else 0, _ptr(bias), _ptr(head_decays), inv_tau, q_scale, k_scale,
+                   _ptr(freq), rot, _ptr(ctx.positions), _ptr(ctx.cu_q), _ptr(binding.state_slots),
+                   binding.state_slots.shape[0], state.data_ptr(), state.stride(0) // 4, _ptr(out), heads, dim, vdim,
+                   _DTYPE_CODE[q.dtype], _stream())
+        return out
+
+    def head_norm_gate(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, heads: int, vdim: int,
+                       eps: float, dtype: torch.dtype) -> torch.Tensor:
+        """[T, heads * vdim] in `dtype`: each head's o (float32) RMS-normed over vdim, times weight (if any), times silu(gate)."""
+        self._check(o, "o", torch.float32, 2)
+        if gate.stride(1) != 1 or gate.dtype != dtype or tuple(gate.shape) != tuple(o.shape):
+            raise KernelError("head_norm_gate: the gate must be a [T, heads * vdim] slice of the activation dtype")
+        out = torch.empty(o.shape, dtype=dtype, device=o.device)
+        self._call("ts_head_norm_gate", _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), o.shape[0], heads, vdim,
+                   eps, _DTYPE_CODE[dtype], _stream())
+        return out
+
+    # ------------------------------------------------------------------ attention over a cached latent
+    def latent_prepare(self, y: torch.Tensor, ctx, binding, q_rank: int, rank: int, rot: int, q_weight: torch.Tensor,
+                       kv_weight: torch.Tensor, eps: float, freq: torch.Tensor) -> torch.Tensor:
+        """
+        y [T, q_rank + rank + rot] (the down projections' output): returns the normed query latent [T, q_rank]
+        and stores [norm(c) | rotated k_rot] into each token's slot of the cache entry.
+        """
+        self._check(y, "y", tuple(_DTYPE_CODE), 2)
+        if y.shape[1] != q_rank + rank + rot:
+            raise KernelError(f"latent_prepare: rows of {y.shape[1]} columns, expected {q_rank + rank + rot}")
+        if binding.k_pool.dtype != y.dtype:
+            raise KernelError(f"cache pool is {binding.k_pool.dtype} but activations are {y.dtype}")
+        c_q = torch.empty((y.shape[0], q_rank), dtype=y.dtype, device=y.device)
+        self._call("ts_latent_prepare", _ptr(y), y.stride(0), q_rank, rank, rot, _ptr(q_weight), _ptr(kv_weight), eps,
+                   _ptr(freq), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(c_q), _ptr(binding.k_pool),
+                   binding.page_stride, binding.entry_offset, binding.page_tokens, binding.num_pages,
+                   _ptr(binding.block_table), binding.table_width, 1 if binding.writes else 0, y.shape[0],
+                   _DTYPE_CODE[y.dtype], _stream())
+        return c_q
+
+    def per_head_linear(self, x: torch.Tensor, w: torch.Tensor, heads: int, head_width: int, k: int,
+                        out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """
+        [T, heads, N]: head h's first k channels of x [T, heads * head_width] times w[h]^T, w [heads, N, k].
+        float32: the engine's FFMA kernel, one product per head in one launch; bfloat16: the library's
+        batched product.  The result may be a strided view.
+        """
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(w, "w", x.dtype, 3)
+        T, N = x.shape[0], w.shape[1]
+        if x.shape[1] != heads * head_width or w.shape[0] != heads or w.shape[2] != k or k > head_width:
+            raise KernelError(f"per_head_linear: x {tuple(x.shape)}, w {tuple(w.shape)} do not fit {heads} heads of {head_width}")
+        if x.dtype == torch.float32:
+            if out_dtype != torch.float32:
+                raise KernelError("per_head_linear: the float32 product has float32 output")
+            out = torch.empty((T, heads, N), dtype=torch.float32, device=x.device)
+            self._call("ts_sgemm_nt_batched", _ptr(x), _ptr(w), _ptr(out), T, N, k, x.stride(0), k, heads * N, heads,
+                       head_width, N * k, N, _stream())
+            return out
+        self.calls["library_bmm"] = self.calls.get("library_bmm", 0) + 1
+        a = x.view(T, heads, head_width)[:, :, :k].transpose(0, 1)          # [heads, T, k]
+        if out_dtype == x.dtype:
+            return torch.bmm(a, w.transpose(1, 2)).transpose(0, 1)
+        return torch.bmm(a, w.transpose(1, 2), out_dtype=out_dtype).transpose(0, 1)
+
+    def latent_attention(self, q_lat: torch.Tensor, q: torch.Tensor, ctx, binding, heads: int, q_head_width: int,
+                         q_rot_offset: int, rank: int, rot: int, freq: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+        """
+        [T, heads, rank] in q's dtype: per head the softmax-weighted sum of the cached latents, scores
+        (q_lat . c + rotated q_rot . k_rot) * scale over the keys the window leaves visible.  q_lat is
+        float32 [T, heads, rank] (any token and head strides); the rotated part of the query is read from
+        q [T, heads * q_head_width] at `q_rot_offset` inside each head and rotated here.
+        """
+        self._check(q, "q", tuple(_DTYPE_CODE), 2)
+        if q_lat.dtype != torch.float32 or q_lat.stride(2) != 1 or tuple(q_lat.shape) != (q.shape[0], heads, rank):
+            raise KernelError("latent_attention: q_lat must be float32 [T, heads, rank] with unit channel stride")
+        if binding.k_pool.dtype != q.dtype:
+            raise KernelError(f"cache pool is {binding.k_pool.dtype} but activations are {q.dtype}")
+        out = torch.empty((q.shape[0], heads, rank), dtype=q.dtype, device=q.device)
+        self._call("ts_latent_attention", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q), q.stride(0), q_head_width,
+                   q_rot_offset, _ptr(freq), _ptr(binding.k_pool), binding.page_stride, binding.entry_offset,
+                   binding.page_tokens, binding.num_pages, _ptr(binding.block_table), binding.table_width,
+                   _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(out), q.shape[0], heads, rank, rot, scale, window,
+                   _DTYPE_CODE[q.dtype], _stream())
+        return out
+
+    # ------------------------------------------------------------------ gated activations, routed experts
+    GATED_ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}
+
+    def gated_activation(self, gate_up: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+        """[T, I] from [T, 2 I] = [gate | up]: silu(g) u, relu(g) u, or the clamped swish g' sigmoid(alpha g') (u' + 1)."""
+        if kind == "silu":
+            return self.silu_mul(gate_up)
+        self._check(gate_up, "gate_up", tuple(_DTYPE_CODE), 2)
+        if gate_up.shape[1] % 2 or kind not in self.GATED_ACTIVATIONS:
+            raise KernelError(f"gated_activation: kind {kind!r} or odd row width {gate_up.shape[1]}")
+        inter = gate_up.shape[1] // 2
+        out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+        self._call("ts_gated_activation", _ptr(gate_up), _ptr(out), gate_up.shape[0], inter, self.GATED_ACTIVATIONS[kind],
+                   limit, alpha, _DTYPE_CODE[gate_up.dtype], _stream())
+        return out
+
+    def moe_route(self, logits: torch.Tensor, bias: torch.Tensor | None, ctx, top: int):
+        """
+        Routing of one step: (chosen [T, top] int32, share [T, top] float32, offsets [E + 1] int32 of the
+        experts' stretches, pair_of_row [T * top], row_of_pair [T * top]).  All on the device; nothing is read back.
+        """
+        self._check(logits, "router logits", torch.float32, 2)
+        T, E = logits.shape
+        dev = logits.device
+        chosen = torch.empty((T, top), dtype=torch.int32, device=dev)
+        share = torch.empty((T, top), dtype=torch.float32, device=dev)
+        counters = torch.zeros((2 * E,), dtype=torch.int32, device=dev)       # per expert: count, then placement cursor
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        pair_of_row = torch.zeros((T * top,), dtype=torch.int32, device=dev)
+        row_of_pair = torch.empty((T * top,), dtype=torch.int32, device=dev)
+        seq_of_token = getattr(ctx, "seq_of_token", None)
+        self._call("ts_moe_route", _ptr(logits), _ptr(bias), _ptr(seq_of_token), _ptr(chosen), _ptr(share), _ptr(counters),
+                   T, E, top, _stream())
+        self._call("ts_moe_arrange", _ptr(chosen), _ptr(counters), counters.data_ptr() + 4 * E, _ptr(offsets),
+                   _ptr(pair_of_row), _ptr(row_of_pair), T * top, E, _stream())
+        return chosen, share, offsets, pair_of_row, row_of_pair
+
+    def moe_linear(self, x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, pair_of_row: torch.Tensor | None, top: int,
+                   pairs: int, activation: str | None = None, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+        """
+        [pairs, N] (or [pairs, N / 2] with a gated `activation`): sorted row r of expert e times w[e]^T,
+        w [E, N, K].  With `pair_of_row` the input row of sorted row r is x[pair_of_row[r] // top]
+        (tokens gathered); without, x[r] (the rows are sorted already).
+        """
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(w, "expert weights", x.dtype, 3)
+        E, N, K = w.shape
+        if x.shape[1] != K:
+            raise KernelError(f"moe_linear: x has {x.shape[1]} columns, the experts {K}")
+        gated = activation is not None
+        out = torch.empty((pairs, N // 2 if gated else N), dtype=x.dtype, device=x.device)
+        self._call("ts_moe_linear", _ptr(x), x.stride(0), _ptr(pair_of_row), top, _ptr(offsets), E, _ptr(w), N, K, _ptr(out),
+                   pairs, 1 if gated else 0, self.GATED_ACTIVATIONS[activation] if gated else 0, limit, alpha,
+                   _DTYPE_CODE[x.dtype], _stream())
+        return out
+
+    def moe_combine(self, y: torch.Tensor, row_of_pair: torch.Tensor, share: torch.Tensor, shared_out: torch.Tensor | None,
+                    num_tokens: int) -> torch.Tensor:
+        """[T, width]: sum over a token's choices of share * y[row of the pair], plus the shared expert's output."""
+        self._check(y, "y", tuple(_DTYPE_CODE), 2)
+        if shared_out is not None:
+            self._check(shared_out, "shared expert output", y.dtype, 2)
+        out = torch.empty((num_tokens, y.shape[1]), dtype=y.dtype, device=y.device)
+        self._call("ts_moe_combine", _ptr(y), _ptr(row_of_pair), _ptr(share), _ptr(shared_out), _ptr(out), num_tokens,
+                   y.shape[1], share.shape[1], _DTYPE_CODE[y.dtype], _stream())
+        return out
+
     def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
         self._check(gate_up, "gate_up", tuple(_DTYPE_CODE), 2)
         if gate_up.shape[1] % 2:
@@ -514,6 +741,11 @@ class Ops:
         """Pools are [pages, entries, kv_heads, page_tokens, head_dim]."""
         self._check(k_pool, "k_pool", tuple(_DTYPE_CODE), 5)
         pages, entries, nkv, page_tokens, hd = k_pool.shape
+        if (hd * k_pool.dtype.itemsize) % 16:                # rows that are no multiple of 16 bytes: torch's own copy
+            k_pool[dst, :, :, :num_slots].copy_(k_pool[src, :, :, :num_slots])
+            if v_pool is not None:
+                v_pool[dst, :, :, :num_slots].copy_(v_pool[src, :, :, :num_slots])
+            return
         self._call("ts_copy_page_slots", _ptr(k_pool), _ptr(v_pool), pages, entries, nkv,
                    page_tokens, hd, k_pool.dtype.itemsize, src, dst,
                    num_slots, _stream())

@@ -33,6 +33,7 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: int = 0           # 0: all keys are kept; w > 0: only the last w
+    values: bool = True       # False: the mixer keeps one row per token and head (no value pool)
 
 
 @dataclass

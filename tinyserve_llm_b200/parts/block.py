@@ -3,6 +3,7 @@ Arrangements: how a block wires its mixer, feed-forward and norms.
 
 "pre_norm" is the reference's decoder layer (model/llama.py:238-253): the residual add is deferred
 into the following norm, so a block takes and returns (branch output, residual stream).
+"sandwich_norm" also norms each sublayer's output and keeps the stream in float32.
 """
 
 from __future__ import annotations
@@ -57,3 +58,63 @@ class PreNormBlock:
         x, residual = self.feed_forward_norm.forward(x, residual)
         x = self.feed_forward.forward(x, ctx)
         return x, residual
+
+
+@register_arrangement("sandwich_norm")
+class SandwichNormBlock:
+    """
+    x = x + norm_b(mixer(norm_a(x))); x = x + norm_d(ffn(norm_c(x))): each sublayer's input and output
+    are normed, the residual stream is float32.  The add of a closed branch and the next opening norm
+    are one kernel: the block hands its last branch on unclosed (`PendingBranch`) and the next block's
+    first norm, or the model's final norm, closes it.  A block without a feed-forward ends after its mixer.
+    """
+
+    takes_token_ids = True
+    takes_embedding_scale = True
+
+    @staticmethod
+    def _members(spec: BlockSpec):
+        members = [
+            ("norm", spec.mixer_norm, spec.mixer_norm_prefix),
+            ("mixer", spec.mixer, spec.mixer_prefix),
+            ("norm", spec.mixer_post_norm, spec.mixer_post_norm_prefix),
+        ]
+        if spec.feed_forward is not None:
+            members += [
+                ("norm", spec.feed_forward_norm, spec.feed_forward_norm_prefix),
+                ("feed_forward", spec.feed_forward, spec.feed_forward_prefix),
+                ("norm", spec.feed_forward_post_norm, spec.feed_forward_post_norm_prefix),
+            ]
+        return members
+
+    @classmethod
+    def declare(cls, spec: BlockSpec) -> dict[str, TensorDecl]:
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and (
+                spec.feed_forward_norm is None or spec.feed_forward_post_norm is None)):
+            raise ValueError("a sandwich_norm block needs a norm before and after each of its sublayers")
+        out: dict[str, TensorDecl] = {}
+        for role, part, prefix in cls._members(spec):
+            for name, decl in part_class(role, part).declare(part).items():
+                out[prefix + name] = decl
+        return out
+
+    def __init__(self, spec: BlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.spec = spec
+        built = [part_class(role, part)(part, _sub(tensors, prefix), rt) for role, part, prefix in self._members(spec)]
+        self.mixer_norm, self.mixer, self.mixer_post_norm = built[:3]
+        self.feed_forward_norm = self.feed_forward = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm = built[3:]
+
+    def forward(self, x, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None,
+                embedding_scale: float = 1.0):
+        from tinyserve_llm_b200.parts.norm import PendingBranch
+        if embedding is not None:
+            h, residual = self.mixer_norm.forward_embedded(embedding, x, embedding_scale)
+        else:
+            h, residual = self.mixer_norm.forward(x, residual)
+        branch = PendingBranch(self.mixer.forward(h, ctx, binding), self.mixer_post_norm)
+        if self.feed_forward is None:
+            return branch, residual
+        h, residual = self.feed_forward_norm.forward(branch, residual)
+        return PendingBranch(self.feed_forward.forward(h, ctx), self.feed_forward_post_norm), residual

@@ -1,0 +1,83 @@
+"""
+Attention over a cached latent: per token the cache keeps c = norm(W_dkv h)[:kv_rank] and one rotated
+key part k_rot shared by all heads; a head's keys and values are W_uk,h c and W_uv,h c.
+
+    c_q = norm(W_dq h),  q = W_uq c_q  laid out per head as [head_dim unrotated | rot_dim rotated]
+    score_h(i, j) = (q_flat,h(i) . W_uk,h c(j) + rot(q_rot,h(i)) . k_rot(j)) * scale
+    y = W_o concat_h( W_uv,h sum_j softmax_j(score_h(i, .)) c(j) )
+
+Since q_flat . (W_uk c) = (W_uk^T q_flat) . c, the engine folds W_uk into the query (one batched
+product per step) and W_uv into the output of the attention (another), and the attention kernel
+works on cache rows [c | k_rot] directly: keys and values of a head are never materialised, in prompts
+as in decoding.  The cache entry is one "kv head" of kv_rank + rot_dim channels without a value pool;
+a window makes it a layer group of its own whose pages are given back as the window passes.
+
+Tensors (local names): dq, dq.norm, uq, dkv, dkv.norm, uk, uv, o.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tinyserve_llm_b200.config.spec import LatentAttentionSpec
+from tinyserve_llm_b200.parts.base import KVNeed, Mixer, Runtime, TensorDecl, part_class, register_part
+from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
+
+MAX_KV_RANK = 512       # csrc/attention_latent.cu: 16 output channels a lane
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    @classmethod
+    def validate(cls, spec: LatentAttentionSpec) -> None:
+        if spec.kv_rank > MAX_KV_RANK:
+            raise ValueError(f"kv_rank={spec.kv_rank} is not supported: the latent attention kernel takes up to {MAX_KV_RANK}")
+        if spec.rot_dim % 2:
+            raise ValueError(f"rot_dim={spec.rot_dim} must be even")
+
+    @classmethod
+    def declare(cls, spec: LatentAttentionSpec) -> dict[str, TensorDecl]:
+        cls.validate(spec)
+        H, D, R, V = spec.num_heads, spec.head_dim, spec.rot_dim, spec.value_dim
+        return {
+            "dq": TensorDecl((spec.q_rank, spec.hidden_size)), "dq.norm": TensorDecl((spec.q_rank,), init="unit"),
+            "uq": TensorDecl((H * (D + R), spec.q_rank)),
+            "dkv": TensorDecl((spec.kv_rank + R, spec.hidden_size)), "dkv.norm": TensorDecl((spec.kv_rank,), init="unit"),
+            "uk": TensorDecl((H * D, spec.kv_rank)), "uv": TensorDecl((H * V, spec.kv_rank)),
+            "o": TensorDecl((spec.hidden_size, H * V)),
+        }
+
+    def __init__(self, spec: LatentAttentionSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        self.validate(spec)
+        H, D, V, rank = spec.num_heads, spec.head_dim, spec.value_dim, spec.kv_rank
+        self.down = Linear(fuse_rows([tensors["dq"], tensors["dkv"]]), rt)          # columns [c_q raw | c raw | k_rot raw]
+        self.q_norm = tensors["dq.norm"].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.kv_norm = tensors["dkv.norm"].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.up_q = Linear(tensors["uq"], rt)
+        # W_uk per head, transposed to [H, rank, D]: the product that folds it into the query reads rows of D
+        self.uk_t = tensors["uk"].to(device=rt.device, dtype=rt.dtype).view(H, D, rank).transpose(1, 2).contiguous()
+        self.uv = tensors["uv"].to(device=rt.device, dtype=rt.dtype).view(H, V, rank).contiguous()
+        self.out = Linear(tensors["o"], rt)
+        self.position = part_class("position", spec.position)(spec.position, {}, rt)
+        if getattr(self.position, "frequencies", None) is None or self.position.dims != spec.rot_dim:
+            raise NotImplementedError("latent attention rotates inside its kernels: it takes a position part with "
+                                      "`frequencies` over exactly rot_dim channels")
+
+    def kv_need(self) -> KVNeed:
+        return KVNeed(1, self.spec.kv_rank + self.spec.rot_dim, self.spec.window, values=False)
+
+    def forward(self, x: torch.Tensor, ctx, binding) -> torch.Tensor:
+        spec, ops = self.spec, self.rt.ops
+        H, D, R, V, rank = spec.num_heads, spec.head_dim, spec.rot_dim, spec.value_dim, spec.kv_rank
+        y = self.down(x)                                                  # [T, q_rank + rank + R]
+        c_q = ops.latent_prepare(y, ctx, binding, spec.q_rank, rank, R, self.q_norm, self.kv_norm, spec.norm_eps,
+                                 self.position.frequencies)              # normed query latent; [c | k_rot] is in the cache
+        q = self.up_q(c_q)                                                # [T, H (D + R)]
+        q_lat = ops.per_head_linear(q, self.uk_t, H, D + R, D)            # float32 [T, H, rank]: W_uk^T q_flat
+        o_lat = ops.latent_attention(q_lat, q, ctx, binding, H, D + R, D, rank, R, self.position.frequencies,
+                                     spec.scale, spec.window)             # [T, H, rank]: softmax-weighted sums of c
+        o = ops.per_head_linear(o_lat.view(-1, H * rank), self.uv, H, rank, rank, out_dtype=x.dtype)   # [T, H, V]
+        return self.out(o.reshape(-1, H * V))

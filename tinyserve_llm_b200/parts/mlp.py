@@ -1,6 +1,8 @@
 """
 Dense gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one projection whose
-output columns are [gate | up].
+output columns are [gate | up].  Activations: silu(g) u (with the products that carry it in their
+epilogue), relu(g) u, and the clamped swish g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
+u' = clamp(u, -limit, limit).
 
 Reference: model/llama.py:77-83 (silu(gate) * up), :215-225 (fused gate_up, down; no biases).
 """
@@ -18,22 +20,27 @@ from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    ACTIVATIONS = ("silu",)
+    ACTIVATIONS = ("silu", "relu", "clamped_swish")
 
     @classmethod
     def declare(cls, spec: GatedMLPSpec) -> dict[str, TensorDecl]:
+        gate, up, down = spec.tensor_names
         return {
-            "gate_proj.weight": TensorDecl((spec.intermediate_size, spec.hidden_size)),
-            "up_proj.weight": TensorDecl((spec.intermediate_size, spec.hidden_size)),
-            "down_proj.weight": TensorDecl((spec.hidden_size, spec.intermediate_size)),
+            gate: TensorDecl((spec.intermediate_size, spec.hidden_size)),
+            up: TensorDecl((spec.intermediate_size, spec.hidden_size)),
+            down: TensorDecl((spec.hidden_size, spec.intermediate_size)),
         }
 
     def __init__(self, spec: GatedMLPSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
         if spec.activation not in self.ACTIVATIONS:
             raise NotImplementedError(f"activation {spec.activation!r} is not supported; have {self.ACTIVATIONS}")
-        self.gate_up = Linear(fuse_rows([tensors["gate_proj.weight"], tensors["up_proj.weight"]]), rt)
-        self.down = Linear(tensors["down_proj.weight"], rt)
+        gate, up, down = spec.tensor_names
+        self.gate_up = Linear(fuse_rows([tensors[gate], tensors[up]]), rt)
+        self.down = Linear(tensors[down], rt)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return self.down(self.rt.ops.linear_swiglu(x, self.gate_up.weight))
+        spec, ops = self.spec, self.rt.ops
+        if spec.activation == "silu":                       # the products with the activation in their epilogue
+            return self.down(ops.linear_swiglu(x, self.gate_up.weight))
+        return self.down(ops.gated_activation(self.gate_up(x), spec.activation, spec.limit, spec.alpha))

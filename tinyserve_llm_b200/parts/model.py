@@ -12,7 +12,8 @@ from __future__ import annotations
 import torch
 
 from tinyserve_llm_b200.config.spec import ModelSpec
-from tinyserve_llm_b200.parts import attention, mlp, norm, rotary  # noqa: F401  (registration)
+from tinyserve_llm_b200.parts import (attention, latent_attention, mlp, norm, recurrence, rotary,  # noqa: F401  (registration)
+                                      routed_experts)
 from tinyserve_llm_b200.parts.base import KVNeed, Runtime, TensorDecl, arrangement_class, part_class
 from tinyserve_llm_b200.parts.block import _sub
 from tinyserve_llm_b200.parts.linear import Linear
@@ -51,7 +52,8 @@ class DecoderModel:
         self._check_run_list()
         # A CUDA graph may replay the model only if no part runs host code that depends on the step.
         self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
-                              for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm))
+                              for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm)
+                              if part is not None)
 
     def _check_run_list(self) -> None:
         writers: dict[int, int] = {}
@@ -86,9 +88,14 @@ class DecoderModel:
         # an arrangement that takes the embedding table reads the token ids itself (its first norm gathers the rows)
         run = self.spec.run
         first = self.blocks[run[0].block] if run else None
-        if first is not None and getattr(first, "takes_token_ids", False):
-            x, residual = first.forward(ctx.token_ids, None, ctx, ctx.binding(run[0]), embedding=self.embedding)
+        scale = float(self.spec.embedding_scale)
+        if first is not None and getattr(first, "takes_token_ids", False) and (
+                scale == 1.0 or getattr(first, "takes_embedding_scale", False)):
+            extra = {"embedding_scale": scale} if scale != 1.0 else {}
+            x, residual = first.forward(ctx.token_ids, None, ctx, ctx.binding(run[0]), embedding=self.embedding, **extra)
             run = run[1:]
+        elif scale != 1.0:
+            raise NotImplementedError("an embedding scale needs a first block whose arrangement takes it")
         else:
             x, residual = self.rt.ops.embedding(self.embedding, ctx.token_ids), None
         for entry in run:

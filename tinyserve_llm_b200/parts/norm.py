@@ -1,5 +1,5 @@
 """
-RMSNorm with the residual add fused in.
+RMSNorm with the residual add fused in; further down, the norm beside a float32 residual stream.
 
 Reference formulas (model/llama.py:52-67): s = f32(x) + f32(residual); the carried residual is s
 rounded to the activation dtype; y = s * rsqrt(mean(s^2) + eps) uses the unrounded sum; the output
@@ -39,3 +39,58 @@ class RMSNorm(Norm):
 
     def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         return self.rt.ops.embed_rmsnorm(table, ids, self.weight, self.eps)
+
+
+class PendingBranch:
+    """
+    A sublayer's output whose closing norm has not been applied yet: the next norm of the stream adds
+    closing(branch) to the stream and norms the sum in one kernel.  Blocks that norm the outputs of
+    their sublayers hand this on as `x`, the next block's first norm (or the model's final norm) takes it.
+    """
+
+    __slots__ = ("tensor", "closing")
+
+    def __init__(self, tensor: torch.Tensor, closing: "StreamRMSNorm") -> None:
+        self.tensor = tensor
+        self.closing = closing
+
+
+@register_part("norm", "rmsnorm_stream")
+class StreamRMSNorm(Norm):
+    """
+    RMS norm beside a float32 residual stream: y = s / sqrt(mean(s^2) + eps) * (offset + w), statistics,
+    weight and stream in float32, y in the activation dtype.  `forward(x, residual)`: x is None (the
+    stream is only normed) or a `PendingBranch` (its closing norm is applied, the result added to the
+    stream, the sum normed).
+    """
+
+    graph_safe = True
+
+    @classmethod
+    def declare(cls, spec) -> dict[str, TensorDecl]:
+        return {spec.weight_name: TensorDecl((spec.size,), init="normal" if spec.weight_offset else "unit")}
+
+    def __init__(self, spec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        w = tensors[spec.weight_name].to(device=rt.device, dtype=torch.float32)
+        self.weight = (w + float(spec.weight_offset)).contiguous() if spec.weight_offset else w.contiguous()
+        self.eps = float(spec.eps)
+
+    def forward(self, x, residual: torch.Tensor | None, rows: torch.Tensor | None = None):
+        if residual is None:
+            raise ValueError("a stream norm needs the residual stream (the first norm starts it from the embedding)")
+        branch, closing = (x.tensor, x.closing.weight) if isinstance(x, PendingBranch) else (None, None)
+        if x is not None and branch is None:
+            raise ValueError("a stream norm takes a PendingBranch (a sublayer's output and its closing norm) or nothing")
+        out = self.rt.ops.stream_norm(branch, closing, residual, self.weight, self.eps, self.rt.dtype, rows=rows)
+        return out, residual
+
+    def close(self, branch: torch.Tensor, residual: torch.Tensor) -> None:
+        """stream += closing(branch), with no norm of the sum."""
+        self.rt.ops.stream_norm(branch, self.weight, residual, None, self.eps, self.rt.dtype)
+
+    def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0):
+        residual = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+        out = self.rt.ops.stream_norm(None, None, residual, self.weight, self.eps, self.rt.dtype, table=table, ids=ids,
+                                      scale=scale)
+        return out, residual

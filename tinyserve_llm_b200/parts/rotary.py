@@ -50,3 +50,23 @@ class Rotary(PositionEncoding):
         if key not in rt.shared:               # one table for all layers with the same settings
             rt.shared[key] = cos_sin_table(spec).to(rt.device)
         self.table = rt.shared[key]
+
+
+@register_part("position", "rotary_inline")
+class InlineRotary(PositionEncoding):
+    """
+    Rotate-half rotation whose angles the kernels compute themselves, position * frequencies[i] in
+    float32 with frequencies[i] = base^(-2i/dims): no table, so no longest position.  Mixers that
+    rotate inside their own kernels read `dims` and `frequencies`.
+    """
+
+    def __init__(self, spec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        if spec.dims <= 0 or spec.dims % 2:
+            raise ValueError(f"rotation over {spec.dims} channels: the number must be positive and even")
+        key = ("rotary_inline", spec)
+        if key not in rt.shared:
+            exponent = torch.arange(0, spec.dims, 2, dtype=torch.float64) / spec.dims
+            rt.shared[key] = (1.0 / (float(spec.base) ** exponent)).to(torch.float32).to(rt.device)
+        self.dims = spec.dims
+        self.frequencies = rt.shared[key]

@@ -1,0 +1,71 @@
+"""
+Routed experts: `num_experts` small gated feed-forward layers of which each token uses the `top`
+with the largest router logits, weighted by the softmax over the chosen logits; a shared expert, if
+the layer has one, runs for every token and is added.
+
+    z = W_r h + b  (float32)      chosen = top-`top` of z      share = softmax(z[chosen])
+    y = sum_j share_j expert_chosen_j(h)  (+ shared(h))
+
+One step runs: the router product, routing and a sort of the (token, choice) pairs by expert on the
+device (nothing is read back, so the step can be replayed from a CUDA graph), one grouped product
+gate/up with the activation in its epilogue, one grouped product down, and the weighted sum.  The
+experts' weights are stacked [experts, 2 ff, width] and [experts, width, ff].
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tinyserve_llm_b200.config.spec import RoutedExpertsSpec
+from tinyserve_llm_b200.parts.base import FeedForward, Runtime, TensorDecl, part_class, register_part
+from tinyserve_llm_b200.parts.linear import Linear
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    @classmethod
+    def declare(cls, spec: RoutedExpertsSpec) -> dict[str, TensorDecl]:
+        if spec.expert is None or not 0 < spec.top <= spec.num_experts:
+            raise ValueError(f"routed experts need an expert description and 0 < top <= experts, got top={spec.top}, "
+                             f"experts={spec.num_experts}")
+        expert_class = part_class("feed_forward", spec.expert)
+        out = {spec.router_name: TensorDecl((spec.num_experts, spec.hidden_size))}
+        if spec.router_bias_name:
+            out[spec.router_bias_name] = TensorDecl((spec.num_experts,))
+        for e in range(spec.num_experts):
+            for name, decl in expert_class.declare(spec.expert).items():
+                out[spec.expert_prefix.format(e) + name] = decl
+        if spec.shared is not None:
+            for name, decl in part_class("feed_forward", spec.shared).declare(spec.shared).items():
+                out[spec.shared_prefix + name] = decl
+        return out
+
+    def __init__(self, spec: RoutedExpertsSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        self.declare(spec)
+        gate, up, down = spec.expert.tensor_names
+        pre = [spec.expert_prefix.format(e) for e in range(spec.num_experts)]
+        to = dict(device=rt.device, dtype=rt.dtype)
+        self.gate_up = torch.stack([torch.cat([tensors[p + gate], tensors[p + up]], dim=0) for p in pre]).to(**to).contiguous()
+        self.down = torch.stack([tensors[p + down] for p in pre]).to(**to).contiguous()
+        self.router = Linear(tensors[spec.router_name], rt)
+        self.router_bias = None
+        if spec.router_bias_name:
+            self.router_bias = tensors[spec.router_bias_name].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.shared = None
+        if spec.shared is not None:
+            sub = {k[len(spec.shared_prefix):]: v for k, v in tensors.items() if k.startswith(spec.shared_prefix)}
+            self.shared = part_class("feed_forward", spec.shared)(spec.shared, sub, rt)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        spec, ops = self.spec, self.rt.ops
+        T, top = x.shape[0], spec.top
+        logits = self.router(x, out_dtype=torch.float32)
+        _, share, offsets, pair_of_row, row_of_pair = ops.moe_route(logits, self.router_bias, ctx, top)
+        e = spec.expert
+        hidden = ops.moe_linear(x, self.gate_up, offsets, pair_of_row, top, T * top, e.activation, e.limit, e.alpha)
+        y = ops.moe_linear(hidden, self.down, offsets, None, top, T * top)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        return ops.moe_combine(y, row_of_pair, share, shared, T)

@@ -87,7 +87,8 @@ def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl], *, optional
                     duplicate.append(name)
                     continue
                 where[name] = f
-                if tuple(declared[name].shape) != entry.shape:
+                want = tuple(declared[name].shape)          # a declared size of -1 is read from the tensor itself
+                if len(want) != len(entry.shape) or any(w not in (-1, g) for w, g in zip(want, entry.shape)):
                     wrong_shape.append((name, entry.shape, tuple(declared[name].shape)))
         missing = [n for n in declared if n not in where]
         if missing or unexpected or wrong_shape or duplicate:

@@ -34,6 +34,9 @@ def random_tensors(declared: Mapping[str, TensorDecl], seed: int, *, std: float 
     """Yields (name, tensor) in declaration order; values are drawn in float32 and rounded to `dtype`."""
     device = torch.device(device)
     for name, decl in declared.items():
+        if any(d < 0 for d in decl.shape):
+            raise ValueError(f"tensor {name!r} takes a size from the checkpoint ({decl.shape}); to draw it, the "
+                             "configuration has to give that size")
         gen = torch.Generator(device=device).manual_seed(_tensor_seed(seed, name))
         t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=gen)
         if decl.init == "unit":
