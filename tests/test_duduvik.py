@@ -83,8 +83,8 @@ class Engine:
         self.runner = StepRunner(self.model, self.manager, self.storage, cuda_graphs=cuda_graphs, sightings_before_capture=1)
         self.got = {}
 
-    def step(self, parts, end=()):
-        """parts: (request, its next tokens); the logits of every fed token are kept."""
+    def step(self, parts, end=(), last_only=False):
+        """parts: (request, its next tokens); the logits of every fed token (or of each request's last) are kept."""
         from tinyserve_llm_b200.engine.step import StepEntry
         entries = []
         for name, tokens in parts:
@@ -92,25 +92,25 @@ class Engine:
                 self.manager.extend(name, tokens)
             else:
                 assert self.manager.admit(name, tokens), f"{name} does not fit"
-            entries.append(StepEntry(name, tokens, list(range(len(tokens)))))
+            entries.append(StepEntry(name, tokens, [len(tokens) - 1] if last_only else list(range(len(tokens)))))
         logits = self.runner.step(entries).cpu().double()
         at = 0
         for e in entries:
             self.manager.commit(e.seq_id, len(e.tokens))
-            self.got.setdefault(e.seq_id, []).append(logits[at:at + len(e.tokens)])
-            at += len(e.tokens)
+            self.got.setdefault(e.seq_id, []).append(logits[at:at + len(e.want)])
+            at += len(e.want)
         for name in end:
             self.manager.release(name)
 
     def logits(self, name):
         return torch.cat(self.got[name])
 
-    def run(self, name, ids, sizes, end=True):
+    def run(self, name, ids, sizes, end=True, last_only=False):
         pos, k = 0, 0
         while pos < len(ids):
             n = min(sizes[k % len(sizes)], len(ids) - pos)
             k += 1
-            self.step([(name, ids[pos:pos + n])], end=[name] if end and pos + n == len(ids) else [])
+            self.step([(name, ids[pos:pos + n])], end=[name] if end and pos + n == len(ids) else [], last_only=last_only)
             pos += n
         return self.logits(name)
 
@@ -187,6 +187,44 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(folders, dtype
         alone[k] = Engine(folders[name, dtype], dtype, page=16, pages=12, slots=3).run(k, ids, [len(ids)])
         if dtype == "float32":
             torch.testing.assert_close(eng.logits(k), alone[k], atol=2e-5, rtol=1e-5)
+
+
+def test_large_steps_on_the_library_grouped_product_also_from_a_graph(folders):
+    """With many (token, expert) pairs the routed layers' bfloat16 products go to the library's grouped product: same logits."""
+    name, dtype = "wide", "bfloat16"
+    ids = ids_of(CONFIGS[name]["vocab"], 150, 7)
+    eng = Engine(folders[name, dtype], dtype, page=16, pages=24, cuda_graphs=True)
+    ops = eng.model.rt.ops
+    old, ops.grouped_mm_min_pairs = ops.grouped_mm_min_pairs, 64
+    try:
+        before = ops.calls.get("library_grouped_mm", 0)
+        got = eng.run("a", ids, [64, 40, 2, 44], last_only=True)                    # 128, 80, 4, 88 pairs
+        assert ops.calls.get("library_grouped_mm", 0) > before and eng.runner.graph_replays >= 3
+    finally:
+        ops.grouped_mm_min_pairs = old
+    close(got, plain_logits(name, folders[name, dtype], ids)[[63, 103, 105, 149]], dtype)
+
+
+def test_decoding_with_the_keys_of_a_token_split_over_several_blocks(folders):
+    """A decoded token far into a window of 300 keys: its keys are split over CTAs and merged; whole prompt and decode agree."""
+    import copy
+    from tinyserve_llm_b200.weights import write_random_model
+    raw = copy.deepcopy(C.LATENT_ONLY)
+    raw["layers"][0]["mixer"]["mask"]["size"] = 300
+    raw["layers"][1]["mixer"]["mask"]["size"] = 1000
+    folder = folders["latent_only", "float32"] + "_long_window"
+    write_random_model(folder, raw, 77, **C.WEIGHTS)
+    ids = ids_of(raw["vocab"], 420, 8)
+    want = plain.forward(raw, read_tensors(folder), ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(folder, dtype, page=16, pages=30)
+        got = eng.run("a", ids, [390] + [1] * 30)
+        assert eng.model.rt.ops.lib.ts_latent_attention_scratch_floats(1, 5, 40, 391) > 0     # the decoded tokens were split
+        if dtype == "float32":
+            torch.testing.assert_close(got, want, atol=3e-4, rtol=1e-4)
+        else:
+            err = (got - want).pow(2).mean(-1).sqrt() / want.std()
+            assert float(err.median()) < 0.03 and float((err > 0.08).double().mean()) < 0.1    # routers as drawn: see `folders`
 
 
 def test_long_decoding_keeps_its_state_and_gives_pages_back(folders):

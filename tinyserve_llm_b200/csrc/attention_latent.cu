@@ -12,15 +12,26 @@
 // ts_latent_prepare: per token, norms the query latent and the key/value latent (plain weights),
 // rotates the shared key part (rotate-half, angle = position * freq[i], float32) and stores [c | k_rot]
 // into the token's slot of the paged cache.
-// ts_latent_attention: one CTA per token and group of up to 8 heads (a warp a head).  Keys come in
+// ts_latent_attention: bfloat16 with sizes it takes runs on the tensor-core kernel of attention_latent_mma.cu;
+// float32 and all other sizes here: one CTA per token and group of up to 8 heads (a warp a head).  Keys come in
 // tiles of 32 into shared memory as float32, shared by the heads; lane j scores key j of the tile, the
 // online softmax runs across the warp, and lane l accumulates channels l, l + 32, ... of the output.
 // A query at position p sees keys max(0, p - window + 1) .. p (window 0: all).  The order of every sum
-// depends on the query's position only.
+// depends on the query's position only.  In a step of few tokens (decoding) a token's keys are split over
+// several CTAs, 128 keys each counted from the window's first key, and a second kernel merges the
+// partial results in key order: again nothing depends on the rest of the batch.
 #include "common.cuh"
+
+bool ts_latent_mma_supported(int rank, int rot);
+int ts_latent_attention_mma_launch(const float* q_lat, long long ql_t, long long ql_h, const void* q, long long q_stride,
+                                   int q_head_width, int q_rot_offset, const float* freq, const void* k_pool,
+                                   KVGeometry geo, const int* block_table, int table_width, const int* positions,
+                                   const int* seq_of_token, void* out, int num_tokens, int heads, int rank, int rot,
+                                   float scale, int window, int split_keys, int splits, float* partial, cudaStream_t stream);
 
 constexpr int LA_WARPS = 8;
 constexpr int LA_KEYS = 32;
+constexpr int LA_SPLIT = 128;       // keys of one CTA when a small step's keys are split over several
 
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ y, long long y_stride, int q_rank, int rank, int rot,
@@ -89,7 +100,7 @@ latent_attention_kernel(const float* __restrict__ q_lat, long long ql_token_stri
                         const float* __restrict__ freq, const T* __restrict__ k_pool, KVGeometry geo,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
                         const int* __restrict__ seq_of_token, T* __restrict__ out, int heads, int rank, int rot, float scale,
-                        int window) {
+                        int window, int split_keys, float* __restrict__ partial) {
     extern __shared__ float smem[];
     const int width = rank + rot, pitch = width + 1;
     float* keys = smem;                                   // [LA_KEYS][pitch]
@@ -119,20 +130,44 @@ latent_attention_kernel(const float* __restrict__ q_lat, long long ql_token_stri
 #pragma unroll
     for (int m = 0; m < MAXR; ++m) o[m] = 0.f;
     float mx = -INFINITY, l = 0.f;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+    // with `split_keys`, CTA z of a token takes keys [first + z * split, first + (z + 1) * split) and leaves a partial result
+    const int lo = first_key + (split_keys > 0 ? (int)blockIdx.z * split_keys : 0);
+    const int hi = split_keys > 0 ? min(pos, lo + split_keys - 1) : pos;
     const int* table = block_table + (long long)seq * table_width;
-    for (int j0 = lo; j0 <= pos; j0 += LA_KEYS) {
+    constexpr int VN = 16 / sizeof(T);
+    const bool vector = width % VN == 0 && ((geo.page_stride | geo.entry_offset) % VN) == 0 &&
+                        (reinterpret_cast<uintptr_t>(k_pool) & 15) == 0;
+    const int chunks = width / VN;
+    for (int j0 = lo; j0 <= hi; j0 += LA_KEYS) {
         __syncthreads();                                  // the tile before has been read (and, first, qs written)
-        const int n = min(LA_KEYS, pos - j0 + 1);
-        for (int e = threadIdx.x; e < n * width; e += blockDim.x) {
-            const int jj = e / width, d = e % width;
-            const int j = j0 + jj;
-            const int page = table[j / geo.page_tokens];
-            float x = 0.f;
-            if (page >= 0 && page < geo.num_pages)
-                x = to_float<T>(k_pool[(long long)page * geo.page_stride + geo.entry_offset +
-                                       (long long)(j % geo.page_tokens) * width + d]);
-            keys[jj * pitch + d] = x;
+        const int n = min(LA_KEYS, hi - j0 + 1);
+        if (vector) {                                     // a warp a key row at a time, 16 bytes a lane
+            for (int jj = warp; jj < n; jj += LA_WARPS) {
+                const int j = j0 + jj;
+                const int page = table[j / geo.page_tokens];
+                const bool in = page >= 0 && page < geo.num_pages;
+                const T* src = k_pool + (long long)(in ? page : 0) * geo.page_stride + geo.entry_offset +
+                               (long long)(j % geo.page_tokens) * width;
+                for (int c = lane; c < chunks; c += 32) {
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (in) v = *reinterpret_cast<const uint4*>(src + c * VN);
+                    const T* el = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) keys[jj * pitch + c * VN + i] = to_float<T>(el[i]);
+                }
+            }
+        } else {
+            for (int e = threadIdx.x; e < n * width; e += blockDim.x) {
+                const int jj = e / width, d = e % width;
+                const int j = j0 + jj;
+                const int page = table[j / geo.page_tokens];
+                float x = 0.f;
+                if (page >= 0 && page < geo.num_pages)
+                    x = to_float<T>(k_pool[(long long)page * geo.page_stride + geo.entry_offset +
+                                           (long long)(j % geo.page_tokens) * width + d]);
+                keys[jj * pitch + d] = x;
+            }
         }
         __syncthreads();
         if (!head) continue;
@@ -161,6 +196,16 @@ latent_attention_kernel(const float* __restrict__ q_lat, long long ql_token_stri
         }
     }
     if (!head) return;
+    if (split_keys > 0) {                                 // [token, head, split]: maximum, sum, then the unscaled output
+        float* dst = partial + (((long long)t * heads + h) * gridDim.z + blockIdx.z) * (rank + 2);
+        if (lane == 0) { dst[0] = mx; dst[1] = l; }
+#pragma unroll
+        for (int m = 0; m < MAXR; ++m) {
+            const int d = lane + 32 * m;
+            if (d < rank) dst[2 + d] = o[m];
+        }
+        return;
+    }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* dst = out + ((long long)t * heads + h) * rank;
 #pragma unroll
@@ -170,14 +215,42 @@ latent_attention_kernel(const float* __restrict__ q_lat, long long ql_token_stri
     }
 }
 
+// Splits of one (token, head) merged in the order of the keys: a split that held no key has sum 0 and counts for nothing.
+template <typename T>
+__global__ void latent_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, long long items, int splits,
+                                      int rank) {
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int lane = threadIdx.x & 31;
+    const float* p = partial + item * splits * (rank + 2);
+    float mx = -INFINITY;
+    for (int z = 0; z < splits; ++z)
+        if (p[(long long)z * (rank + 2) + 1] > 0.f) mx = fmaxf(mx, p[(long long)z * (rank + 2)]);
+    float total = 0.f;
+    for (int z = 0; z < splits; ++z) {
+        const float l = p[(long long)z * (rank + 2) + 1];
+        if (l > 0.f) total += l * expf(p[(long long)z * (rank + 2)] - mx);
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    for (int d = lane; d < rank; d += 32) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float* q = p + (long long)z * (rank + 2);
+            if (q[1] > 0.f) acc += q[2 + d] * expf(q[0] - mx);
+        }
+        out[item * rank + d] = from_float<T>(acc * inv);
+    }
+}
+
 template <typename T>
 static int launch_latent(const float* q_lat, long long ql_t, long long ql_h, const void* q, long long q_stride,
                          int q_head_width, int q_rot_offset, const float* freq, const void* k_pool, KVGeometry geo,
                          const int* block_table, int table_width, const int* positions, const int* seq_of_token, void* out,
-                         int num_tokens, int heads, int rank, int rot, float scale, int window, cudaStream_t stream) {
+                         int num_tokens, int heads, int rank, int rot, float scale, int window, int split_keys, int splits,
+                         float* partial, cudaStream_t stream) {
     const int width = rank + rot;
     const size_t smem = (size_t)(LA_KEYS * (width + 1) + LA_WARPS * width) * sizeof(float);
-    dim3 grid(num_tokens, (heads + LA_WARPS - 1) / LA_WARPS);
+    dim3 grid(num_tokens, (heads + LA_WARPS - 1) / LA_WARPS, split_keys > 0 ? splits : 1);
 #define TS_LATENT(MAXR)                                                                                              \
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
@@ -185,14 +258,28 @@ static int launch_latent(const float* q_lat, long long ql_t, long long ql_h, con
                                  (int)smem);                                                                         \
         latent_attention_kernel<T, MAXR><<<grid, LA_WARPS * 32, smem, stream>>>(                                     \
             q_lat, ql_t, ql_h, (const T*)q, q_stride, q_head_width, q_rot_offset, freq, (const T*)k_pool, geo,       \
-            block_table, table_width, positions, seq_of_token, (T*)out, heads, rank, rot, scale, window);            \
+            block_table, table_width, positions, seq_of_token, (T*)out, heads, rank, rot, scale, window, split_keys, \
+            partial);                                                                                                \
     } while (0)
     if (rank <= 128) TS_LATENT(4);
     else if (rank <= 256) TS_LATENT(8);
     else TS_LATENT(16);
 #undef TS_LATENT
     TS_LAUNCH_CHECK("latent_attention");
+    if (split_keys > 0) {
+        const long long items = (long long)num_tokens * heads;
+        latent_combine_kernel<T><<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(partial, (T*)out, items, splits, rank);
+        TS_LAUNCH_CHECK("latent_attention (combine)");
+    }
     return 0;
+}
+
+// How many floats of scratch a call with these sizes needs (0: the step is large enough to run without splits).
+TS_API long long ts_latent_attention_scratch_floats(int num_tokens, int heads, int rank, int max_keys) {
+    const int groups = (heads + LA_WARPS - 1) / LA_WARPS;
+    if ((long long)num_tokens * groups >= 148 || max_keys <= 2 * LA_SPLIT) return 0;
+    const int splits = (max_keys + LA_SPLIT - 1) / LA_SPLIT;
+    return (long long)num_tokens * heads * splits * (rank + 2);
 }
 
 TS_API int ts_latent_attention(const float* q_lat, long long ql_token_stride, long long ql_head_stride, const void* q,
@@ -200,7 +287,8 @@ TS_API int ts_latent_attention(const float* q_lat, long long ql_token_stride, lo
                                const void* k_pool, long long page_stride, long long entry_offset, int page_tokens,
                                int num_pages, const int* block_table, int table_width, const int* positions,
                                const int* seq_of_token, void* out, int num_tokens, int heads, int rank, int rot,
-                               float scale, int window, int dtype, cudaStream_t stream) {
+                               float scale, int window, int max_keys, float* scratch, long long scratch_floats, int dtype,
+                               cudaStream_t stream) {
     TS_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && rot >= 0 && rot % 2 == 0, "latent_attention: bad sizes");
     TS_REQUIRE(rank <= 512, "latent_attention: a latent of %d channels is not supported (up to 512)", rank);
     TS_REQUIRE(rank + rot <= 1024, "latent_attention: cache rows of %d channels are not supported", rank + rot);
@@ -208,13 +296,39 @@ TS_API int ts_latent_attention(const float* q_lat, long long ql_token_stride, lo
     TS_REQUIRE(num_tokens <= 2147483647 && heads <= 65535 * LA_WARPS, "latent_attention: grid too large");
     if (num_tokens == 0) return 0;
     KVGeometry geo{page_stride, entry_offset, page_tokens, num_pages};
+    // a step of few tokens (decoding) spreads each token's keys over several CTAs, LA_SPLIT keys each, counted from the
+    // window's first key; `max_keys` bounds the keys any token of the step sees
+    const long long need = ts_latent_attention_scratch_floats(num_tokens, heads, rank, max_keys);
+    int split_keys = 0, splits = 1;
+    if (need > 0) {
+        TS_REQUIRE(scratch != nullptr && scratch_floats >= need, "latent_attention: %lld floats of scratch needed, %lld given",
+                   need, scratch_floats);
+        split_keys = LA_SPLIT;
+        splits = (max_keys + LA_SPLIT - 1) / LA_SPLIT;
+        TS_REQUIRE(splits <= 65535, "latent_attention: %d keys need too many splits", max_keys);
+    }
+    if (dtype == TS_BF16 && ts_latent_mma_supported(rank, rot) && page_stride % 8 == 0 && entry_offset % 8 == 0 &&
+        (uintptr_t)k_pool % 16 == 0) {
+        // bfloat16 with sizes the tensor-core kernel takes: heads as the rows of mma.sync products
+        if (ts_latent_attention_mma_launch(q_lat, ql_token_stride, ql_head_stride, q, q_stride, q_head_width, q_rot_offset,
+                                           freq, k_pool, geo, block_table, table_width, positions, seq_of_token, out,
+                                           num_tokens, heads, rank, rot, scale, window, split_keys, splits, scratch, stream))
+            return 1;
+        if (split_keys > 0) {
+            const long long items = (long long)num_tokens * heads;
+            latent_combine_kernel<__nv_bfloat16><<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(
+                scratch, (__nv_bfloat16*)out, items, splits, rank);
+            TS_LAUNCH_CHECK("latent_attention (combine)");
+        }
+        return 0;
+    }
     if (dtype == TS_F32)
         return launch_latent<float>(q_lat, ql_token_stride, ql_head_stride, q, q_stride, q_head_width, q_rot_offset, freq,
                                     k_pool, geo, block_table, table_width, positions, seq_of_token, out, num_tokens, heads,
-                                    rank, rot, scale, window, stream);
+                                    rank, rot, scale, window, split_keys, splits, scratch, stream);
     if (dtype == TS_BF16)
         return launch_latent<__nv_bfloat16>(q_lat, ql_token_stride, ql_head_stride, q, q_stride, q_head_width, q_rot_offset,
                                             freq, k_pool, geo, block_table, table_width, positions, seq_of_token, out,
-                                            num_tokens, heads, rank, rot, scale, window, stream);
+                                            num_tokens, heads, rank, rot, scale, window, split_keys, splits, scratch, stream);
     return ts_fail("latent_attention: unknown dtype code %d", dtype);
 }

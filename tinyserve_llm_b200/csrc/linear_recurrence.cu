@@ -10,19 +10,20 @@
 // projections on is float32: rotation, decays, the state, the sums.
 //
 // One kernel serves prompts, portions of prompts and single decoded tokens: a CTA owns one request,
-// one head and 32 value channels, reads the state from the request's slot, walks over the request's
+// one head and 16 value channels, reads the state from the request's slot, walks over the request's
 // tokens of this step in order and writes the state back.  The arithmetic of a token does not depend
 // on where the step was cut or on what else is in the batch.  Tokens are staged 16 at a time
 // (rotation and decays computed by all threads in parallel); inside a tile no thread waits for
-// another: thread (r, j) holds rows r, r + 8, ... of column j of S and leaves its share of o_t[j] in
-// shared memory, and the eight shares are added up in a fixed order after the tile.
+// another: thread (r, j) holds a run of rows of column j of S (read from the staged tile four
+// channels a load) and leaves its share of o_t[j] in shared memory, and the sixteen shares are added
+// up in a fixed order after the tile.
 //
 // A second kernel norms each head's o over the value channels (with or without a weight),
 // multiplies by silu(gate) and rounds to the activation dtype for the output projection.
 #include "common.cuh"
 
-constexpr int LR_ROWGROUPS = 8;     // warps of a CTA: warp r holds rows r, r + 8, ... of the state
-constexpr int LR_COLS = 32;         // value channels of a CTA
+constexpr int LR_ROWGROUPS = 16;    // thread (r, j) holds rows r * MAXM .. r * MAXM + MAXM - 1 of column j of the state
+constexpr int LR_COLS = 16;         // value channels of a CTA
 constexpr int LR_TILE = 16;         // tokens staged at a time
 
 struct RecurrenceArgs {
@@ -46,12 +47,15 @@ __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - l
 template <typename T, int MAXM>
 __global__ void __launch_bounds__(LR_ROWGROUPS * LR_COLS)
 linear_recurrence_kernel(RecurrenceArgs p) {
-    extern __shared__ float smem[];
+    // staged rows are padded with zeros to LR_ROWGROUPS * MAXM channels: the inner loop needs no bound and reads
+    // four channels a load
+    constexpr int PITCH = LR_ROWGROUPS * MAXM;
+    extern __shared__ __align__(16) float smem[];
     const int dim = p.dim, vdim = p.vdim;
-    float* q_s = smem;                                   // [LR_TILE][dim]
-    float* k_s = q_s + LR_TILE * dim;                    // [LR_TILE][dim]
-    float* a_s = k_s + LR_TILE * dim;                    // [LR_TILE][dim]
-    float* v_s = a_s + LR_TILE * dim;                    // [LR_TILE][LR_COLS]
+    float* q_s = smem;                                   // [LR_TILE][PITCH]
+    float* k_s = q_s + LR_TILE * PITCH;
+    float* a_s = k_s + LR_TILE * PITCH;
+    float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][LR_COLS]
     float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
     const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
     const int slot = p.slots[seq];
@@ -63,7 +67,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     float S[MAXM];
 #pragma unroll
     for (int m = 0; m < MAXM; ++m) {
-        const int i = r + LR_ROWGROUPS * m;
+        const int i = r * MAXM + m;
         S[m] = (live && i < dim) ? st[(long long)i * vdim + j] : 0.f;
     }
     const T* q = (const T*)p.q;
@@ -74,31 +78,40 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     for (int t0 = begin; t0 < end; t0 += LR_TILE) {
         const int n = min(LR_TILE, end - t0);
         __syncthreads();                                 // the tile before has been read
-        for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-            const int tt = e / dim, i = e % dim;
-            const long long t = t0 + tt;
-            const T* qr = q + t * p.q_stride + (long long)h * dim;
-            const T* kr = k + t * p.k_stride + (long long)h * dim;
-            float qv = to_float<T>(qr[i]), kv = to_float<T>(kr[i]);
-            if (p.freq && i < p.rot_dims) {
-                const int f = i < half ? i : i - half;
-                const float angle = (float)p.positions[t] * p.freq[f];
-                float sn, cs;
-                sincosf(angle, &sn, &cs);
-                const int other = i < half ? i + half : i - half;
-                const float qo = to_float<T>(qr[other]), ko = to_float<T>(kr[other]);
-                // first half: u cos - v sin; second half: v cos + u sin
-                qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
-                kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+        // a fixed number of rounds, unrolled: the loads of a whole tile are under way together
+#pragma unroll
+        for (int round = 0; round < LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS); ++round) {
+            const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
+            const int tt = e / PITCH, i = e % PITCH;
+            float qv = 0.f, kv = 0.f, a = 0.f;
+            if (tt < n && i < dim) {
+                const long long t = t0 + tt;
+                const T* qr = q + t * p.q_stride + (long long)h * dim;
+                const T* kr = k + t * p.k_stride + (long long)h * dim;
+                qv = to_float<T>(qr[i]);
+                kv = to_float<T>(kr[i]);
+                if (p.freq && i < p.rot_dims) {
+                    const int f = i < half ? i : i - half;
+                    const float angle = (float)p.positions[t] * p.freq[f];
+                    float sn, cs;
+                    sincosf(angle, &sn, &cs);
+                    const int other = i < half ? i + half : i - half;
+                    const float qo = to_float<T>(qr[other]), ko = to_float<T>(kr[other]);
+                    // first half: u cos - v sin; second half: v cos + u sin
+                    qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
+                    kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+                }
+                qv *= p.q_scale;
+                kv *= p.k_scale;
+                a = head_decay;
+                if (p.z) {
+                    float x = p.z[t * p.z_stride + (long long)h * dim + i];
+                    if (p.bias) x += p.bias[h * dim + i];
+                    a = expf(log_sigmoid(x) * p.inv_tau);
+                }
             }
-            q_s[e] = qv * p.q_scale;
-            k_s[e] = kv * p.k_scale;
-            float a = head_decay;
-            if (p.z) {
-                float x = p.z[t * p.z_stride + (long long)h * dim + i];
-                if (p.bias) x += p.bias[h * dim + i];
-                a = expf(log_sigmoid(x) * p.inv_tau);
-            }
+            q_s[e] = qv;
+            k_s[e] = kv;
             a_s[e] = a;
         }
         for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
@@ -108,16 +121,19 @@ linear_recurrence_kernel(RecurrenceArgs p) {
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
             const float vj = v_s[tt * LR_COLS + jj];
-            const float* qt = q_s + tt * dim;
-            const float* kt = k_s + tt * dim;
-            const float* at = a_s + tt * dim;
+            const float4* qt = reinterpret_cast<const float4*>(q_s + tt * PITCH + r * MAXM);
+            const float4* kt = reinterpret_cast<const float4*>(k_s + tt * PITCH + r * MAXM);
+            const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + r * MAXM);
             float acc = 0.f;
 #pragma unroll
-            for (int m = 0; m < MAXM; ++m) {
-                const int i = r + LR_ROWGROUPS * m;
-                if (i < dim) {
-                    S[m] = fmaf(at[i], S[m], kt[i] * vj);
-                    acc = fmaf(S[m], qt[i], acc);
+            for (int m4 = 0; m4 < MAXM / 4; ++m4) {
+                const float4 q4 = qt[m4], k4 = kt[m4], a4 = at[m4];
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int m = 4 * m4 + c;
+                    S[m] = fmaf(aa[c], S[m], kk[c] * vj);
+                    acc = fmaf(S[m], qq[c], acc);
                 }
             }
             part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
@@ -134,7 +150,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     }
 #pragma unroll
     for (int m = 0; m < MAXM; ++m) {
-        const int i = r + LR_ROWGROUPS * m;
+        const int i = r * MAXM + m;
         if (live && i < dim) st[(long long)i * vdim + j] = S[m];
     }
 }
@@ -142,9 +158,10 @@ linear_recurrence_kernel(RecurrenceArgs p) {
 template <typename T>
 static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t stream) {
     dim3 grid((p.vdim + LR_COLS - 1) / LR_COLS, p.heads, num_seqs);
-    const size_t smem = (size_t)(3 * LR_TILE * p.dim + LR_TILE * LR_COLS + LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);
 #define TS_RECURRENCE(MAXM)                                                                                        \
     do {                                                                                                           \
+        const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * LR_COLS +                       \
+                                     LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);                            \
         if (smem > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
@@ -152,8 +169,7 @@ static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t
     } while (0)
     if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4);
     else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8);
-    else if (p.dim <= 16 * LR_ROWGROUPS) TS_RECURRENCE(16);
-    else TS_RECURRENCE(32);
+    else TS_RECURRENCE(16);
 #undef TS_RECURRENCE
     TS_LAUNCH_CHECK("linear_recurrence");
     return 0;
@@ -166,8 +182,8 @@ TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, lon
                                 float* state, long long slot_stride, float* out, int heads, int dim, int vdim,
                                 int dtype, cudaStream_t stream) {
     TS_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && num_seqs >= 0, "linear_recurrence: bad sizes");
-    TS_REQUIRE(dim <= 32 * LR_ROWGROUPS, "linear_recurrence: %d key channels a head are not supported (up to %d)", dim,
-               32 * LR_ROWGROUPS);
+    TS_REQUIRE(dim <= 16 * LR_ROWGROUPS, "linear_recurrence: %d key channels a head are not supported (up to %d)", dim,
+               16 * LR_ROWGROUPS);
     TS_REQUIRE(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0, "linear_recurrence: rotation over %d of %d channels",
                rot_dims, dim);
     TS_REQUIRE((z != nullptr) != (head_decay != nullptr), "linear_recurrence: either decay logits or one decay per head");

@@ -10,8 +10,10 @@
 //                    W [experts, N, K].  Tiles of 32 pairs x 64 columns, FFMA with float32 sums over k
 //                    in ascending order (a pair's result does not depend on its row or on the batch).
 //                    With `gated`, W_e holds gate rows then up rows and the epilogue applies the gated
-//                    activation (see activation.cu for the kinds) before it stores.  Input rows are
+//                    activation (the kinds are listed below) before it stores.  Input rows are
 //                    gathered by token for the first product; the second reads the sorted rows.
+//                    A step of up to 64 pairs takes a weight-streaming kernel instead (further down); large
+//                    bfloat16 steps may be given to the library's grouped product by the caller.
 //   ts_moe_combine   out[t] = sum_j share[t, j] * y[row of (t, j)] (+ the shared expert's output), in the
 //                    order of j, float32, rounded once.
 #include "common.cuh"
@@ -202,6 +204,77 @@ moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __rest
     }
 }
 
+// The same product for a step of a few tokens (decoding): a row tile is up to 8 pairs of one expert,
+// kept in shared memory; a warp owns output columns and streams their weight rows once, 16 bytes a
+// lane at a time, for all rows of the tile at once.  A row's sum over k has one order, whatever the batch.
+constexpr int SR = 8, SWARPS = 8;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(SWARPS * 32)
+moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ pair_of_row, int top,
+                       const int* __restrict__ offsets, int experts, const T* __restrict__ w, int N, int K,
+                       T* __restrict__ y, int out_cols, int cols_per_cta, int kind, float limit, float alpha) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    T* xs = reinterpret_cast<T*>(raw);                    // [SR][K]
+    constexpr int VN = 16 / sizeof(T);
+    int tile = blockIdx.y, e = 0, first = 0, last = 0;
+    for (; e < experts; ++e) {
+        first = offsets[e]; last = offsets[e + 1];
+        const int tiles = (last - first + SR - 1) / SR;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (e == experts) return;
+    const int row0 = first + tile * SR;
+    const int nrows = min(SR, last - row0);
+    for (int i = threadIdx.x; i < SR * (K / VN); i += blockDim.x) {
+        const int r = i / (K / VN), c = i % (K / VN);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+            const int src = pair_of_row ? pair_of_row[row0 + r] / top : row0 + r;
+            v = *reinterpret_cast<const uint4*>(x + (long long)src * x_stride + c * VN);
+        }
+        *reinterpret_cast<uint4*>(xs + (long long)r * K + c * VN) = v;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* we = w + (long long)e * N * K;
+    const int half = GATED ? N / 2 : 0;
+    const int col_end = min(out_cols, (int)(blockIdx.x + 1) * cols_per_cta);
+    for (int col = blockIdx.x * cols_per_cta + warp; col < col_end; col += SWARPS) {
+        float acc[SR], accu[SR];
+#pragma unroll
+        for (int r = 0; r < SR; ++r) acc[r] = accu[r] = 0.f;
+        const T* wrow = we + (long long)col * K;
+        const T* urow = we + (long long)(half + col) * K;
+        for (int c = lane * VN; c < K; c += 32 * VN) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wrow + c);
+            uint4 uv = make_uint4(0, 0, 0, 0);
+            if (GATED) uv = *reinterpret_cast<const uint4*>(urow + c);
+            const T* wl = reinterpret_cast<const T*>(&wv);
+            const T* ul = reinterpret_cast<const T*>(&uv);
+#pragma unroll
+            for (int r = 0; r < SR; ++r) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xs + (long long)r * K + c);
+                const T* xl = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) {
+                    const float xf = to_float<T>(xl[i]);
+                    acc[r] = fmaf(xf, to_float<T>(wl[i]), acc[r]);
+                    if (GATED) accu[r] = fmaf(xf, to_float<T>(ul[i]), accu[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < SR; ++r) {
+            const float g = warp_sum(acc[r]);
+            const float u = GATED ? warp_sum(accu[r]) : 0.f;
+            if (lane == 0 && r < nrows)
+                y[(long long)(row0 + r) * out_cols + col] = from_float<T>(GATED ? gated_activation(kind, g, u, limit, alpha) : g);
+        }
+    }
+}
+
 TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_row, int top, const int* offsets,
                          int experts, const void* w, int N, int K, void* y, int pairs, int gated, int kind, float limit,
                          float alpha, int dtype, cudaStream_t stream) {
@@ -209,6 +282,28 @@ TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_r
     TS_REQUIRE(!gated || N % 2 == 0, "moe_linear: a gated weight holds gate and up rows of equal number");
     if (pairs <= 0) return 0;
     const int out_cols = gated ? N / 2 : N;
+    const int elem = dtype == TS_F32 ? 4 : 2, vn = 16 / elem;
+    if (pairs <= 64 && K % vn == 0 && (x_stride * elem) % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+        (size_t)SR * K * elem <= 200 * 1024 && (dtype == TS_F32 || dtype == TS_BF16)) {
+        const int tiles = (pairs + SR - 1) / SR + experts;
+        const int cols_per_cta = out_cols <= 256 ? 32 : 64;
+        dim3 sgrid((out_cols + cols_per_cta - 1) / cols_per_cta, tiles);
+        const size_t smem = (size_t)SR * K * elem;
+#define TS_MOE_ROWS(TYPE, G)                                                                                           \
+        do {                                                                                                           \
+            if (smem > 48 * 1024)                                                                                      \
+                cudaFuncSetAttribute(moe_linear_rows_kernel<TYPE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                     (int)smem);                                                                       \
+            moe_linear_rows_kernel<TYPE, G><<<sgrid, SWARPS * 32, smem, stream>>>(                                     \
+                (const TYPE*)x, x_stride, pair_of_row, top, offsets, experts, (const TYPE*)w, N, K, (TYPE*)y, out_cols, \
+                cols_per_cta, kind, limit, alpha);                                                                     \
+        } while (0)
+        if (dtype == TS_F32) { if (gated) TS_MOE_ROWS(float, true); else TS_MOE_ROWS(float, false); }
+        else { if (gated) TS_MOE_ROWS(__nv_bfloat16, true); else TS_MOE_ROWS(__nv_bfloat16, false); }
+#undef TS_MOE_ROWS
+        TS_LAUNCH_CHECK("moe_linear");
+        return 0;
+    }
     const int row_tiles = (pairs + GM - 1) / GM + experts;       // every expert may end in a ragged tile
     TS_REQUIRE(row_tiles <= 65535, "moe_linear: %d pairs need more than 65535 row tiles", pairs);
     dim3 grid((out_cols + GN - 1) / GN, row_tiles);

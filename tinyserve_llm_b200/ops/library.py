@@ -52,7 +52,9 @@ _SIGNATURES = {
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiip"),
     "ts_head_norm_gate": ("int", "pplppiiifip"),
     "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
-    "ts_latent_attention": ("int", "pllpliipplliipipppiiiifiip"),
+    "ts_latent_attention": ("int", "pllpliipplliipipppiiiifiiplip"),
+    "ts_latent_attention_scratch_floats": ("long long", "iiii"),
+    "ts_set_latent_mma": ("void", "i"),
     "ts_moe_route": ("int", "ppppppiiip"),
     "ts_moe_arrange": ("int", "ppppppiip"),
     "ts_moe_linear": ("int", "plpipipiipiiiffip"),
@@ -138,6 +140,8 @@ class Ops:
         self.set_chaining(os.environ.get("TINYSERVE_B200_CHAINING", "1") != "0")
         # TINYSERVE_B200_PREFILL=mma keeps prompt attention on the mma.sync kernel (the tcgen05 one is the default)
         self.tcgen05_attention = os.environ.get("TINYSERVE_B200_PREFILL", "tcgen05") != "mma"
+        # TINYSERVE_B200_LATENT=ffma keeps attention over a cached latent off the tensor-core kernel
+        self.lib.ts_set_latent_mma(0 if os.environ.get("TINYSERVE_B200_LATENT", "mma") == "ffma" else 1)
         # From this many rows of x the gate/up product runs on the engine's tcgen05 kernel with SwiGLU in its
         # epilogue: measured on a B200 against the library product plus an activation kernel, it is 8 to 13 % faster
         # from 512 rows on with Llama 3.2 1B's sizes (3B and 3.1 8B: the same or faster), and slower between 257 and
@@ -147,6 +151,8 @@ class Ops:
         # 3.2 1B's sizes, whole decode steps: 4 to 6 % faster than the library product plus the activation kernel at 12,
         # 16, 24 and 32 rows, since the weights go through the cp.async ring)
         self.swiglu_skinny_rows = self.skinny_max_rows
+        # from this many (token, expert) pairs a routed feed-forward's bfloat16 products go to the library's grouped product
+        self.grouped_mm_min_pairs = int(os.environ.get("TINYSERVE_B200_GROUPED_PAIRS", "256"))
 
     def set_chaining(self, enabled: bool) -> None:
         self.chaining = bool(enabled)
@@ -545,11 +551,28 @@ class Ops:
         if binding.k_pool.dtype != q.dtype:
             raise KernelError(f"cache pool is {binding.k_pool.dtype} but activations are {q.dtype}")
         out = torch.empty((q.shape[0], heads, rank), dtype=q.dtype, device=q.device)
+        # the most keys a token of this step sees: bounded by the window and by the longest request (a replayed step: its shape's bound)
+        longest = getattr(ctx, "max_ctx_len", None)
+        if longest is None:
+            longest = int(ctx.positions.max()) + 1
+        max_keys = min(window, longest) if window > 0 else longest
+        floats = int(self.lib.ts_latent_attention_scratch_floats(q.shape[0], heads, rank, max_keys))
+        scratch = None
+        if floats:
+            store = getattr(ctx, "scratch", None)
+            key = ("latent_attention", floats)
+            scratch = store.get(key) if store is not None else None
+            if scratch is None:
+                scratch = torch.empty((floats,), dtype=torch.float32, device=q.device)
+                if store is not None:
+                    store[key] = scratch
         self._call("ts_latent_attention", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q), q.stride(0), q_head_width,
                    q_rot_offset, _ptr(freq), _ptr(binding.k_pool), binding.page_stride, binding.entry_offset,
                    binding.page_tokens, binding.num_pages, _ptr(binding.block_table), binding.table_width,
                    _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(out), q.shape[0], heads, rank, rot, scale, window,
-                   _DTYPE_CODE[q.dtype], _stream())
+                   max_keys, _ptr(scratch), floats, _DTYPE_CODE[q.dtype], _stream())
+        if floats:
+            self.launches += 1                               # the kernel that merges the splits
         return out
 
     # ------------------------------------------------------------------ gated activations, routed experts
@@ -602,6 +625,14 @@ class Ops:
         if x.shape[1] != K:
             raise KernelError(f"moe_linear: x has {x.shape[1]} columns, the experts {K}")
         gated = activation is not None
+        if (x.dtype == torch.bfloat16 and pairs >= self.grouped_mm_min_pairs and K % 8 == 0 and N % 8 == 0
+                and hasattr(torch, "_grouped_mm")):
+            # many pairs: the library's grouped product (bfloat16 tensor cores, the experts' stretches given on the
+            # device), then the gate as a kernel of its own; few pairs and float32 stay on the engine's kernels
+            self.calls["library_grouped_mm"] = self.calls.get("library_grouped_mm", 0) + 1
+            rows = x if pair_of_row is None else x.index_select(0, torch.div(pair_of_row, top, rounding_mode="floor"))
+            full = torch._grouped_mm(rows, w.transpose(1, 2), offs=offsets[1:])
+            return self.gated_activation(full, activation, limit, alpha) if gated else full
         out = torch.empty((pairs, N // 2 if gated else N), dtype=x.dtype, device=x.device)
         self._call("ts_moe_linear", _ptr(x), x.stride(0), _ptr(pair_of_row), top, _ptr(offsets), E, _ptr(w), N, K, _ptr(out),
                    pairs, 1 if gated else 0, self.GATED_ACTIVATIONS[activation] if gated else 0, limit, alpha,

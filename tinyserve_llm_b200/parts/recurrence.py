@@ -27,7 +27,7 @@ from tinyserve_llm_b200.config.spec import LinearRecurrenceSpec
 from tinyserve_llm_b200.parts.base import Mixer, Runtime, TensorDecl, part_class, register_part
 from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
-MAX_KEY_DIM = 256       # csrc/linear_recurrence.cu: 8 row groups x 32 rows in registers
+MAX_KEY_DIM = 256       # csrc/linear_recurrence.cu: 16 row groups x 16 rows in registers
 
 
 @register_part("mixer", "linear_recurrence")
