@@ -298,8 +298,9 @@ def _latent_case(dtype, page, window, positions_and_contexts, rank=24, rot=8, he
     return out.cpu().double(), want
 
 
+@pytest.mark.parametrize("rank, rot", [(24, 8), (64, 16), (96, 32)])        # the second and third: sizes the tensor-core kernel takes
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_latent_attention_sees_exactly_its_window(dtype):
+def test_latent_attention_sees_exactly_its_window(dtype, rank, rot):
     """
     One key dominates head 0: queries whose window still holds it return its latent, the next query
     does not.  The key sits at a page's last slot and the queries come both as a prompt portion and
@@ -308,7 +309,7 @@ def test_latent_attention_sees_exactly_its_window(dtype):
     page, window, key = 16, 37, 31                                                  # last slot of the second page
     inside, outside = key + window - 1, key + window                               # the last query that sees it, the first that does not
     cases = [(list(range(inside - 3, outside + 3)), outside + 3), ([outside], outside + 1), ([inside], inside + 1), ([4], 5)]
-    got, want = _latent_case(dtype, page, window, cases, special=(0, key))
+    got, want = _latent_case(dtype, page, window, cases, rank=rank, rot=rot, special=(0, key))
     tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.04, rtol=0.02)
     torch.testing.assert_close(got, want, **tol)
     seen = got[:, 0, 0]                                                             # channel 0 of head 0: 30 if the key is seen
@@ -317,10 +318,15 @@ def test_latent_attention_sees_exactly_its_window(dtype):
     assert abs(float(seen[6])) < 5 and abs(float(seen[7])) < 5 and abs(float(seen[8])) < 5
 
 
-def test_latent_attention_far_keys_without_a_window_and_first_tokens():
-    """No window: a key hundreds of positions back, among many, is found; position 0 sees itself only."""
-    got, want = _latent_case(torch.float32, 16, 0, [([0, 1, 2, 499], 500), ([250], 251)], special=(0, 3))
-    torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-5)
+@pytest.mark.parametrize("dtype, rank, rot, heads", [(torch.float32, 24, 8, 3), (torch.bfloat16, 64, 16, 3), (torch.bfloat16, 128, 32, 19)])
+def test_latent_attention_far_keys_without_a_window_and_first_tokens(dtype, rank, rot, heads):
+    """
+    No window: a key hundreds of positions back, among many, is found; position 0 sees itself only.  The
+    step is small, so each token's keys are split over several CTAs and merged (19 heads: two groups of rows).
+    """
+    got, want = _latent_case(dtype, 16, 0, [([0, 1, 2, 499], 500), ([250], 251)], rank=rank, rot=rot, heads=heads, special=(0, 3))
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.04, rtol=0.02)
+    torch.testing.assert_close(got, want, **tol)
     assert float(got[3, 0, 0]) > 25 and abs(float(got[0, 0, 0])) < 5
 
 

@@ -25,6 +25,7 @@
 constexpr int LR_ROWGROUPS = 16;    // thread (r, j) holds rows r * MAXM .. r * MAXM + MAXM - 1 of column j of the state
 constexpr int LR_COLS = 16;         // value channels of a CTA
 constexpr int LR_TILE = 16;         // tokens staged at a time
+static_assert(LR_TILE * LR_COLS == LR_ROWGROUPS * LR_COLS, "a thread stages one value of v a tile");
 
 struct RecurrenceArgs {
     const void* q; const void* k; const void* v;      // activation dtype, rows of the step's tokens
@@ -57,6 +58,8 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     float* a_s = k_s + LR_TILE * PITCH;
     float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][LR_COLS]
     float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
+    float* bias_s = part + LR_TILE * LR_ROWGROUPS * LR_COLS;   // [PITCH] this head's decay bias
+    float* freq_s = bias_s + PITCH;                      // [PITCH] rotation frequency of each channel
     const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
     const int slot = p.slots[seq];
     const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
@@ -75,49 +78,75 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     const T* v = (const T*)p.v;
     const int half = p.rot_dims / 2;
     const float head_decay = p.head_decay ? p.head_decay[h] : 1.f;
-    for (int t0 = begin; t0 < end; t0 += LR_TILE) {
-        const int n = min(LR_TILE, end - t0);
-        __syncthreads();                                 // the tile before has been read
-        // a fixed number of rounds, unrolled: the loads of a whole tile are under way together
+    for (int i = threadIdx.x; i < PITCH; i += blockDim.x) {        // read once: the staging below touches no global memory
+        bias_s[i] = (p.bias && i < dim) ? p.bias[h * dim + i] : 0.f;
+        freq_s[i] = (p.freq && i < p.rot_dims) ? p.freq[i < half ? i : i - half] : 0.f;
+    }
+    // What a tile needs from global memory is asked for one tile ahead and held in registers while the tile
+    // before it is worked on; rotation and decays are computed from the registers into shared memory.
+    constexpr int ROUNDS = LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS);
+    T raw_q[ROUNDS], raw_k[ROUNDS], raw_qo[ROUNDS], raw_ko[ROUNDS], raw_v;   // as loaded: converting would wait for the load
+    float raw_z[ROUNDS];
+    int raw_pos[ROUNDS];
+    auto fetch = [&](int t0, int n) {
 #pragma unroll
-        for (int round = 0; round < LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS); ++round) {
+        for (int round = 0; round < ROUNDS; ++round) {
             const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
             const int tt = e / PITCH, i = e % PITCH;
-            float qv = 0.f, kv = 0.f, a = 0.f;
+            raw_q[round] = raw_k[round] = raw_qo[round] = raw_ko[round] = from_float<T>(0.f);
+            raw_z[round] = 0.f;
+            raw_pos[round] = 0;
             if (tt < n && i < dim) {
                 const long long t = t0 + tt;
                 const T* qr = q + t * p.q_stride + (long long)h * dim;
                 const T* kr = k + t * p.k_stride + (long long)h * dim;
-                qv = to_float<T>(qr[i]);
-                kv = to_float<T>(kr[i]);
+                raw_q[round] = qr[i];
+                raw_k[round] = kr[i];
                 if (p.freq && i < p.rot_dims) {
-                    const int f = i < half ? i : i - half;
-                    const float angle = (float)p.positions[t] * p.freq[f];
-                    float sn, cs;
-                    sincosf(angle, &sn, &cs);
                     const int other = i < half ? i + half : i - half;
-                    const float qo = to_float<T>(qr[other]), ko = to_float<T>(kr[other]);
+                    raw_qo[round] = qr[other];
+                    raw_ko[round] = kr[other];
+                    raw_pos[round] = p.positions[t];
+                }
+                if (p.z) raw_z[round] = p.z[t * p.z_stride + (long long)h * dim + i];
+            }
+        }
+        const int tt = threadIdx.x / LR_COLS, c = threadIdx.x % LR_COLS;       // LR_TILE * LR_COLS = one value a thread
+        raw_v = from_float<T>(0.f);
+        if (tt < n && j0 + c < vdim) raw_v = v[(long long)(t0 + tt) * p.v_stride + (long long)h * vdim + j0 + c];
+    };
+    fetch(begin, min(LR_TILE, end - begin));
+    for (int t0 = begin; t0 < end; t0 += LR_TILE) {
+        const int n = min(LR_TILE, end - t0);
+        __syncthreads();                                 // the tile before has been read
+#pragma unroll
+        for (int round = 0; round < ROUNDS; ++round) {
+            const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
+            const int tt = e / PITCH, i = e % PITCH;
+            float qv = 0.f, kv = 0.f, a = 0.f;
+            if (tt < n && i < dim) {
+                qv = to_float<T>(raw_q[round]);
+                kv = to_float<T>(raw_k[round]);
+                if (p.freq && i < p.rot_dims) {
+                    float sn, cs;
+                    sincosf((float)raw_pos[round] * freq_s[i], &sn, &cs);
                     // first half: u cos - v sin; second half: v cos + u sin
-                    qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
-                    kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+                    qv = i < half ? qv * cs - to_float<T>(raw_qo[round]) * sn : qv * cs + to_float<T>(raw_qo[round]) * sn;
+                    kv = i < half ? kv * cs - to_float<T>(raw_ko[round]) * sn : kv * cs + to_float<T>(raw_ko[round]) * sn;
                 }
                 qv *= p.q_scale;
                 kv *= p.k_scale;
                 a = head_decay;
                 if (p.z) {
-                    float x = p.z[t * p.z_stride + (long long)h * dim + i];
-                    if (p.bias) x += p.bias[h * dim + i];
-                    a = expf(log_sigmoid(x) * p.inv_tau);
+                    a = expf(log_sigmoid(raw_z[round] + bias_s[i]) * p.inv_tau);
                 }
             }
             q_s[e] = qv;
             k_s[e] = kv;
             a_s[e] = a;
         }
-        for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
-            const int tt = e / LR_COLS, c = e % LR_COLS;
-            v_s[e] = (j0 + c < vdim) ? to_float<T>(v[(long long)(t0 + tt) * p.v_stride + (long long)h * vdim + j0 + c]) : 0.f;
-        }
+        v_s[threadIdx.x] = to_float<T>(raw_v);
+        if (t0 + LR_TILE < end) fetch(t0 + LR_TILE, min(LR_TILE, end - t0 - LR_TILE));   // under way during this tile's work
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
             const float vj = v_s[tt * LR_COLS + jj];
@@ -161,7 +190,7 @@ static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t
 #define TS_RECURRENCE(MAXM)                                                                                        \
     do {                                                                                                           \
         const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * LR_COLS +                       \
-                                     LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);                            \
+                                     LR_TILE * LR_ROWGROUPS * LR_COLS + 2 * LR_ROWGROUPS * MAXM) * sizeof(float);  \
         if (smem > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
