@@ -216,29 +216,38 @@ latent_attention_kernel(const float* __restrict__ q_lat, long long ql_token_stri
 }
 
 // Splits of one (token, head) merged in the order of the keys: a split that held no key has sum 0 and counts for nothing.
+// One CTA an item: the first warp turns the splits' maxima and sums into one weight a split, then every thread adds up
+// its channels over the splits.
+constexpr int LC_MAX_SPLITS = 1024;
+
 template <typename T>
-__global__ void latent_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, long long items, int splits,
-                                      int rank) {
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= items) return;
-    const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, long long items, int splits, int rank) {
+    __shared__ float weight[LC_MAX_SPLITS];
+    const long long item = blockIdx.x;
     const float* p = partial + item * splits * (rank + 2);
-    float mx = -INFINITY;
-    for (int z = 0; z < splits; ++z)
-        if (p[(long long)z * (rank + 2) + 1] > 0.f) mx = fmaxf(mx, p[(long long)z * (rank + 2)]);
-    float total = 0.f;
-    for (int z = 0; z < splits; ++z) {
-        const float l = p[(long long)z * (rank + 2) + 1];
-        if (l > 0.f) total += l * expf(p[(long long)z * (rank + 2)] - mx);
-    }
-    const float inv = total > 0.f ? 1.f / total : 0.f;
-    for (int d = lane; d < rank; d += 32) {
-        float acc = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float* q = p + (long long)z * (rank + 2);
-            if (q[1] > 0.f) acc += q[2 + d] * expf(q[0] - mx);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float mx = -INFINITY;
+        for (int z = lane; z < splits; z += 32)
+            if (p[(long long)z * (rank + 2) + 1] > 0.f) mx = fmaxf(mx, p[(long long)z * (rank + 2)]);
+        mx = warp_max(mx);
+        float total = 0.f;
+        for (int z = lane; z < splits; z += 32) {
+            const float l = p[(long long)z * (rank + 2) + 1];
+            const float w = l > 0.f ? expf(p[(long long)z * (rank + 2)] - mx) : 0.f;
+            weight[z] = w;
+            total += l * w;
         }
-        out[item * rank + d] = from_float<T>(acc * inv);
+        total = warp_sum(total);
+        const float inv = total > 0.f ? 1.f / total : 0.f;
+        for (int z = lane; z < splits; z += 32) weight[z] *= inv;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) acc = fmaf(p[(long long)z * (rank + 2) + 2 + d], weight[z], acc);
+        out[item * rank + d] = from_float<T>(acc);
     }
 }
 
@@ -268,7 +277,7 @@ static int launch_latent(const float* q_lat, long long ql_t, long long ql_h, con
     TS_LAUNCH_CHECK("latent_attention");
     if (split_keys > 0) {
         const long long items = (long long)num_tokens * heads;
-        latent_combine_kernel<T><<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(partial, (T*)out, items, splits, rank);
+        latent_combine_kernel<T><<<(unsigned)items, 128, 0, stream>>>(partial, (T*)out, items, splits, rank);
         TS_LAUNCH_CHECK("latent_attention (combine)");
     }
     return 0;
@@ -305,7 +314,7 @@ TS_API int ts_latent_attention(const float* q_lat, long long ql_token_stride, lo
                    need, scratch_floats);
         split_keys = LA_SPLIT;
         splits = (max_keys + LA_SPLIT - 1) / LA_SPLIT;
-        TS_REQUIRE(splits <= 65535, "latent_attention: %d keys need too many splits", max_keys);
+        TS_REQUIRE(splits <= LC_MAX_SPLITS, "latent_attention: %d keys need more than %d splits", max_keys, LC_MAX_SPLITS);
     }
     if (dtype == TS_BF16 && ts_latent_mma_supported(rank, rot) && page_stride % 8 == 0 && entry_offset % 8 == 0 &&
         (uintptr_t)k_pool % 16 == 0) {
@@ -316,7 +325,7 @@ TS_API int ts_latent_attention(const float* q_lat, long long ql_token_stride, lo
             return 1;
         if (split_keys > 0) {
             const long long items = (long long)num_tokens * heads;
-            latent_combine_kernel<__nv_bfloat16><<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(
+            latent_combine_kernel<__nv_bfloat16><<<(unsigned)items, 128, 0, stream>>>(
                 scratch, (__nv_bfloat16*)out, items, splits, rank);
             TS_LAUNCH_CHECK("latent_attention (combine)");
         }

@@ -247,6 +247,7 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
         for (int r = 0; r < SR; ++r) acc[r] = accu[r] = 0.f;
         const T* wrow = we + (long long)col * K;
         const T* urow = we + (long long)(half + col) * K;
+#pragma unroll 2
         for (int c = lane * VN; c < K; c += 32 * VN) {
             const uint4 wv = *reinterpret_cast<const uint4*>(wrow + c);
             uint4 uv = make_uint4(0, 0, 0, 0);
@@ -255,6 +256,7 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
             const T* ul = reinterpret_cast<const T*>(&uv);
 #pragma unroll
             for (int r = 0; r < SR; ++r) {
+                if (r >= nrows) break;                    // a decoding step often gives an expert one pair
                 const uint4 xv = *reinterpret_cast<const uint4*>(xs + (long long)r * K + c);
                 const T* xl = reinterpret_cast<const T*>(&xv);
 #pragma unroll
