@@ -318,7 +318,8 @@ def test_latent_attention_sees_exactly_its_window(dtype, rank, rot):
     assert abs(float(seen[6])) < 5 and abs(float(seen[7])) < 5 and abs(float(seen[8])) < 5
 
 
-@pytest.mark.parametrize("dtype, rank, rot, heads", [(torch.float32, 24, 8, 3), (torch.bfloat16, 64, 16, 3), (torch.bfloat16, 128, 32, 19)])
+@pytest.mark.parametrize("dtype, rank, rot, heads", [(torch.float32, 24, 8, 3), (torch.float32, 40, 4, 11), (torch.bfloat16, 64, 16, 3),
+                                                     (torch.bfloat16, 128, 32, 19)])
 def test_latent_attention_far_keys_without_a_window_and_first_tokens(dtype, rank, rot, heads):
     """
     No window: a key hundreds of positions back, among many, is found; position 0 sees itself only.  The

@@ -62,8 +62,10 @@ TS_API int ts_stream_norm(const void* branch, const float* w_close, float* strea
     TS_REQUIRE(!(ids && (!table || branch)), "stream_norm: token ids need the table and exclude a branch");
     TS_REQUIRE(width <= 48 * 1024, "stream_norm: rows of %d elements are not supported", width);
     if (count == 0) return 0;
-    // a thread handles about four elements a pass: few rows (decoding) are bound by the chain of loads, not by their number
-    const int threads = width >= 4096 ? 1024 : width >= 2048 ? 512 : width >= 1024 ? 256 : 128;
+    // few rows (decoding) are bound by the chain of loads, not by their number: about four elements a thread and pass;
+    // many rows keep more CTAs on an SM instead
+    const int wide = width >= 4096 ? 1024 : width >= 2048 ? 512 : width >= 1024 ? 256 : 128;
+    const int threads = count <= 512 ? wide : (width >= 1024 ? 256 : 128);
     const size_t smem = (size_t)(width + 32) * sizeof(float);
     const int write = rows ? 0 : 1;
 #define TS_STREAM_NORM(TYPE)                                                                                      \
