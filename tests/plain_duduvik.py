@@ -9,8 +9,6 @@ Notation: h is a sublayer's input [T, width]; p_t the position of token t in its
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -39,10 +37,6 @@ def rotate_half(x: torch.Tensor, positions: torch.Tensor, dims: int, base: float
     cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
     a, b = x[..., :half], x[..., half:dims]
     return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., dims:]), dim=-1)
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 # ---------------------------------------------------------------------------------------------- mixers
