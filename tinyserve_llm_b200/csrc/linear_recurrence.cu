@@ -12,8 +12,9 @@
 // One kernel serves prompts, portions of prompts and single decoded tokens: a CTA owns one request,
 // one head and 16 value channels, reads the state from the request's slot, walks over the request's
 // tokens of this step in order and writes the state back.  The arithmetic of a token does not depend
-// on where the step was cut or on what else is in the batch.  Tokens are staged 16 at a time
-// (rotation and decays computed by all threads in parallel); inside a tile no thread waits for
+// on where the step was cut or on what else is in the batch.  A first kernel computes what enters
+// the recurrence (rotated and scaled q and k, the decays) once per token, head and channel; the scan
+// stages 16 tokens of it at a time, fetched one tile ahead.  Inside a tile no thread waits for
 // another: thread (r, j) holds a run of rows of column j of S (read from the staged tile four
 // channels a load) and leaves its share of o_t[j] in shared memory, and the sixteen shares are added
 // up in a fixed order after the tile.
@@ -27,23 +28,49 @@ constexpr int LR_COLS = 16;         // value channels of a CTA
 constexpr int LR_TILE = 16;         // tokens staged at a time
 static_assert(LR_TILE * LR_COLS == LR_ROWGROUPS * LR_COLS, "a thread stages one value of v a tile");
 
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// What enters the recurrence, computed once per token, head and key channel (the scan's CTAs of one head all read it):
+// prepared[0] = rotated, scaled q; prepared[1] = rotated, scaled k; prepared[2] = the decay a.  Each [tokens, heads * dim].
+template <typename T>
+__global__ void recurrence_prepare_kernel(const T* __restrict__ q, const T* __restrict__ k, long long q_stride,
+                                          long long k_stride, const float* __restrict__ z, long long z_stride,
+                                          const float* __restrict__ bias, const float* __restrict__ head_decay,
+                                          float inv_tau, float q_scale, float k_scale, const float* __restrict__ freq,
+                                          int rot_dims, const int* __restrict__ positions, float* __restrict__ prepared,
+                                          long long total, int heads, int dim) {
+    const int width = heads * dim, half = rot_dims / 2;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long t = e / width;
+        const int c = (int)(e % width), h = c / dim, i = c % dim;
+        const T* qr = q + t * q_stride + (long long)h * dim;
+        const T* kr = k + t * k_stride + (long long)h * dim;
+        float qv = to_float<T>(qr[i]), kv = to_float<T>(kr[i]);
+        if (freq && i < rot_dims) {
+            const int f = i < half ? i : i - half, other = i < half ? i + half : i - half;
+            float sn, cs;
+            sincosf((float)positions[t] * freq[f], &sn, &cs);
+            const float qo = to_float<T>(qr[other]), ko = to_float<T>(kr[other]);
+            // first half: u cos - v sin; second half: v cos + u sin
+            qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
+            kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+        }
+        float a = head_decay ? head_decay[h] : 1.f;
+        if (z) a = expf(log_sigmoid(z[t * z_stride + c] + (bias ? bias[c] : 0.f)) * inv_tau);
+        prepared[e] = qv * q_scale;
+        prepared[total + e] = kv * k_scale;
+        prepared[2 * total + e] = a;
+    }
+}
+
 struct RecurrenceArgs {
-    const void* q; const void* k; const void* v;      // activation dtype, rows of the step's tokens
-    long long q_stride, k_stride, v_stride;           // elements between tokens
-    const float* z; long long z_stride;               // decay logits [tokens, heads * dim] (mode 1)
-    const float* bias;                                // [heads * dim] added to z (mode 1), may be null
-    const float* head_decay;                          // [heads] (mode 0)
-    float inv_tau;
-    float q_scale, k_scale;
-    const float* freq; int rot_dims;                  // rotation of q and k (freq null: none)
-    const int* positions;
+    const float* prepared; long long total;           // [3][tokens, heads * dim]: q, k, decay as they enter the recurrence
+    const void* v; long long v_stride;                // activation dtype, elements between tokens
     const int* cu_q; const int* slots;
     float* state; long long slot_stride;              // floats between slots; a slot holds [heads, dim, vdim]
     float* out;                                       // [tokens, heads * vdim] float32
     int heads, dim, vdim;
 };
-
-__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 template <typename T, int MAXM>
 __global__ void __launch_bounds__(LR_ROWGROUPS * LR_COLS)
@@ -58,8 +85,6 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     float* a_s = k_s + LR_TILE * PITCH;
     float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][LR_COLS]
     float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
-    float* bias_s = part + LR_TILE * LR_ROWGROUPS * LR_COLS;   // [PITCH] this head's decay bias
-    float* freq_s = bias_s + PITCH;                      // [PITCH] rotation frequency of each channel
     const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
     const int slot = p.slots[seq];
     const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
@@ -73,42 +98,24 @@ linear_recurrence_kernel(RecurrenceArgs p) {
         const int i = r * MAXM + m;
         S[m] = (live && i < dim) ? st[(long long)i * vdim + j] : 0.f;
     }
-    const T* q = (const T*)p.q;
-    const T* k = (const T*)p.k;
     const T* v = (const T*)p.v;
-    const int half = p.rot_dims / 2;
-    const float head_decay = p.head_decay ? p.head_decay[h] : 1.f;
-    for (int i = threadIdx.x; i < PITCH; i += blockDim.x) {        // read once: the staging below touches no global memory
-        bias_s[i] = (p.bias && i < dim) ? p.bias[h * dim + i] : 0.f;
-        freq_s[i] = (p.freq && i < p.rot_dims) ? p.freq[i < half ? i : i - half] : 0.f;
-    }
+    const long long row_width = (long long)p.heads * dim;
     // What a tile needs from global memory is asked for one tile ahead and held in registers while the tile
-    // before it is worked on; rotation and decays are computed from the registers into shared memory.
+    // before it is worked on.
     constexpr int ROUNDS = LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS);
-    T raw_q[ROUNDS], raw_k[ROUNDS], raw_qo[ROUNDS], raw_ko[ROUNDS], raw_v;   // as loaded: converting would wait for the load
-    float raw_z[ROUNDS];
-    int raw_pos[ROUNDS];
+    float raw_q[ROUNDS], raw_k[ROUNDS], raw_a[ROUNDS];
+    T raw_v;                                             // as loaded: converting would wait for the load
     auto fetch = [&](int t0, int n) {
 #pragma unroll
         for (int round = 0; round < ROUNDS; ++round) {
             const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
             const int tt = e / PITCH, i = e % PITCH;
-            raw_q[round] = raw_k[round] = raw_qo[round] = raw_ko[round] = from_float<T>(0.f);
-            raw_z[round] = 0.f;
-            raw_pos[round] = 0;
+            raw_q[round] = raw_k[round] = raw_a[round] = 0.f;
             if (tt < n && i < dim) {
-                const long long t = t0 + tt;
-                const T* qr = q + t * p.q_stride + (long long)h * dim;
-                const T* kr = k + t * p.k_stride + (long long)h * dim;
-                raw_q[round] = qr[i];
-                raw_k[round] = kr[i];
-                if (p.freq && i < p.rot_dims) {
-                    const int other = i < half ? i + half : i - half;
-                    raw_qo[round] = qr[other];
-                    raw_ko[round] = kr[other];
-                    raw_pos[round] = p.positions[t];
-                }
-                if (p.z) raw_z[round] = p.z[t * p.z_stride + (long long)h * dim + i];
+                const long long at = (long long)(t0 + tt) * row_width + (long long)h * dim + i;
+                raw_q[round] = p.prepared[at];
+                raw_k[round] = p.prepared[p.total + at];
+                raw_a[round] = p.prepared[2 * p.total + at];
             }
         }
         const int tt = threadIdx.x / LR_COLS, c = threadIdx.x % LR_COLS;       // LR_TILE * LR_COLS = one value a thread
@@ -122,28 +129,9 @@ linear_recurrence_kernel(RecurrenceArgs p) {
 #pragma unroll
         for (int round = 0; round < ROUNDS; ++round) {
             const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
-            const int tt = e / PITCH, i = e % PITCH;
-            float qv = 0.f, kv = 0.f, a = 0.f;
-            if (tt < n && i < dim) {
-                qv = to_float<T>(raw_q[round]);
-                kv = to_float<T>(raw_k[round]);
-                if (p.freq && i < p.rot_dims) {
-                    float sn, cs;
-                    sincosf((float)raw_pos[round] * freq_s[i], &sn, &cs);
-                    // first half: u cos - v sin; second half: v cos + u sin
-                    qv = i < half ? qv * cs - to_float<T>(raw_qo[round]) * sn : qv * cs + to_float<T>(raw_qo[round]) * sn;
-                    kv = i < half ? kv * cs - to_float<T>(raw_ko[round]) * sn : kv * cs + to_float<T>(raw_ko[round]) * sn;
-                }
-                qv *= p.q_scale;
-                kv *= p.k_scale;
-                a = head_decay;
-                if (p.z) {
-                    a = expf(log_sigmoid(raw_z[round] + bias_s[i]) * p.inv_tau);
-                }
-            }
-            q_s[e] = qv;
-            k_s[e] = kv;
-            a_s[e] = a;
+            q_s[e] = raw_q[round];
+            k_s[e] = raw_k[round];
+            a_s[e] = raw_a[round];
         }
         v_s[threadIdx.x] = to_float<T>(raw_v);
         if (t0 + LR_TILE < end) fetch(t0 + LR_TILE, min(LR_TILE, end - t0 - LR_TILE));   // under way during this tile's work
@@ -190,7 +178,7 @@ static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t
 #define TS_RECURRENCE(MAXM)                                                                                        \
     do {                                                                                                           \
         const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * LR_COLS +                       \
-                                     LR_TILE * LR_ROWGROUPS * LR_COLS + 2 * LR_ROWGROUPS * MAXM) * sizeof(float);  \
+                                     LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);                            \
         if (smem > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                  (int)smem);                                                                       \
@@ -209,8 +197,8 @@ TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, lon
                                 const float* head_decay, float inv_tau, float q_scale, float k_scale, const float* freq,
                                 int rot_dims, const int* positions, const int* cu_q, const int* slots, int num_seqs,
                                 float* state, long long slot_stride, float* out, int heads, int dim, int vdim,
-                                int dtype, cudaStream_t stream) {
-    TS_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && num_seqs >= 0, "linear_recurrence: bad sizes");
+                                int num_tokens, float* prepared, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && num_seqs >= 0 && num_tokens >= 0, "linear_recurrence: bad sizes");
     TS_REQUIRE(dim <= 16 * LR_ROWGROUPS, "linear_recurrence: %d key channels a head are not supported (up to %d)", dim,
                16 * LR_ROWGROUPS);
     TS_REQUIRE(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0, "linear_recurrence: rotation over %d of %d channels",
@@ -218,12 +206,24 @@ TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, lon
     TS_REQUIRE((z != nullptr) != (head_decay != nullptr), "linear_recurrence: either decay logits or one decay per head");
     TS_REQUIRE(slot_stride >= (long long)heads * dim * vdim, "linear_recurrence: a state slot is too small");
     TS_REQUIRE(num_seqs <= 65535 && heads <= 65535, "linear_recurrence: grid too large");
-    if (num_seqs == 0) return 0;
-    RecurrenceArgs p{q, k, v, q_stride, k_stride, v_stride, z, z_stride, bias, head_decay, inv_tau, q_scale, k_scale,
-                     rot_dims > 0 ? freq : nullptr, rot_dims, positions, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
+    TS_REQUIRE(prepared != nullptr || num_tokens == 0, "linear_recurrence: no room for the prepared inputs");
+    if (num_seqs == 0 || num_tokens == 0) return 0;
+    const long long total = (long long)num_tokens * heads * dim;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    const float* fr = rot_dims > 0 ? freq : nullptr;
+    if (dtype == TS_F32)
+        recurrence_prepare_kernel<float><<<blocks, 256, 0, stream>>>((const float*)q, (const float*)k, q_stride, k_stride, z,
+            z_stride, bias, head_decay, inv_tau, q_scale, k_scale, fr, rot_dims, positions, prepared, total, heads, dim);
+    else if (dtype == TS_BF16)
+        recurrence_prepare_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
+            q_stride, k_stride, z, z_stride, bias, head_decay, inv_tau, q_scale, k_scale, fr, rot_dims, positions, prepared,
+            total, heads, dim);
+    else
+        return ts_fail("linear_recurrence: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("linear_recurrence (prepare)");
+    RecurrenceArgs p{prepared, total, v, v_stride, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
     if (dtype == TS_F32) return launch_recurrence<float>(p, num_seqs, stream);
-    if (dtype == TS_BF16) return launch_recurrence<__nv_bfloat16>(p, num_seqs, stream);
-    return ts_fail("linear_recurrence: unknown dtype code %d", dtype);
+    return launch_recurrence<__nv_bfloat16>(p, num_seqs, stream);
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); one warp a (token, head).

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "ts_skinny_linear": ("int", "pppiiilliip"),
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
     "ts_stream_norm": ("int", "ppppppiifppifip"),
-    "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiip"),
+    "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
     "ts_head_norm_gate": ("int", "pplppiiifip"),
     "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
     "ts_latent_attention": ("int", "pllpliipplliipipppiiiifiiplip"),
@@ -474,11 +474,13 @@ class Ops:
         if position is not None:
             freq, rot = position.frequencies, position.dims
         out = torch.empty((T, heads * vdim), dtype=torch.float32, device=q.device)
+        prepared = torch.empty((3, T, heads * dim), dtype=torch.float32, device=q.device)   # q, k, decays as they enter the scan
         self._call("ts_linear_recurrence", _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(z),
                    z.stride(0) if z is not None else 0, _ptr(bias), _ptr(head_decays), inv_tau, q_scale, k_scale,
                    _ptr(freq), rot, _ptr(ctx.positions), _ptr(ctx.cu_q), _ptr(binding.state_slots),
                    binding.state_slots.shape[0], state.data_ptr(), state.stride(0) // 4, _ptr(out), heads, dim, vdim,
-                   _DTYPE_CODE[q.dtype], _stream())
+                   T, _ptr(prepared), _DTYPE_CODE[q.dtype], _stream())
+        self.launches += 1                                   # the kernel that prepares the scan's inputs
         return out
 
     def head_norm_gate(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, heads: int, vdim: int,
