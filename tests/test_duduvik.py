@@ -471,6 +471,28 @@ def test_routed_experts_part(dtype, experts, top, shared):
     torch.testing.assert_close(got, want, **tol)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 100, 640])        # the weight-streaming kernel, the library + activation kernel, tcgen05
+@pytest.mark.parametrize("activation, limit, alpha", [("relu", 0.0, 1.0), ("clamped_swish", 0.7, 1.702)])
+def test_gated_products_with_the_activation_in_their_epilogue(rows, activation, limit, alpha):
+    from tinyserve_llm_b200.ops import get_ops
+    ops = get_ops()
+    g = torch.Generator().manual_seed(rows)
+    K, inter = 256, 200
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, generator=g) * 0.08).to(torch.bfloat16)
+    got = ops.linear_gated(x.cuda(), w.cuda(), activation, limit, alpha).cpu().double()
+    y = x.double() @ w.double().T
+    gate, up = y[:, :inter], y[:, inter:]
+    if activation == "relu":
+        want = torch.relu(gate) * up
+    else:
+        gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+        want = gate * torch.sigmoid(alpha * gate) * (up + 1.0)
+    torch.testing.assert_close(got, want, atol=0.03, rtol=0.03)
+    x32, w32 = x.float().cuda(), w.float().cuda()
+    torch.testing.assert_close(ops.linear_gated(x32, w32, activation, limit, alpha).cpu().double(), want, atol=1e-4, rtol=1e-4)
+
+
 def test_router_ties_go_to_the_lower_index_and_shares_are_a_softmax():
     from types import SimpleNamespace
     from tinyserve_llm_b200.ops import get_ops

@@ -52,6 +52,20 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { re
 template <typename T>
 __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
 
+// Gated activations of feed-forward layers, act(gate, up):  0: silu(g) u;  1: relu(g) u;
+// 2: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+enum { TS_ACT_SILU = 0, TS_ACT_RELU = 1, TS_ACT_CLAMPED_SWISH = 2 };
+
+__device__ __forceinline__ float ts_gated_activation(int kind, float g, float u, float limit, float alpha) {
+    if (kind == TS_ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (kind == TS_ACT_CLAMPED_SWISH) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -114,6 +114,8 @@ struct GemmParams {
     int inter;            // SwiGLU: rows of W per half
     int out_f32;
     int* error;
+    int act;              // gated epilogue: the activation (TS_ACT_* of common.cuh; 0 = SiLU) and its constants
+    float act_limit, act_alpha;
 };
 
 template <int EPI, int BN, int STAGES>
@@ -242,7 +244,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
                         for (int e = 0; e < 8; ++e) {
                             const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
                             const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
-                            v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                            if (p.act == TS_ACT_SILU) v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                            else v[e] = ts_gated_activation(p.act, g, u, p.act_limit, p.act_alpha);
                         }
                         if (n0 + c + 8 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0) {
                             uint4 packed;
@@ -477,7 +480,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_pair_kernel(const __grid
                         for (int e = 0; e < 8; ++e) {
                             const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
                             const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
-                            v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                            if (p.act == TS_ACT_SILU) v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                            else v[e] = ts_gated_activation(p.act, g, u, p.act_limit, p.act_alpha);
                         }
                         if (n0 + c + 8 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0) {
                             uint4 packed;
@@ -587,8 +591,25 @@ TS_API int ts_gemm_tcgen05_supported(const void* W, const void* x, int M, int N,
 // y[M, N] = x[M, K] . W[N, K]^T (epilogue 0; out_dtype TS_BF16 or TS_F32), or y[M, N/2] = the SwiGLU of
 // it with W = [gate rows | up rows] (epilogue 1, bfloat16 out).  `error` points to an int the host can
 // read (0: fine; 1, 2, 3: a producer, MMA or epilogue wait ran out of time).
+static int gemm_tcgen05_launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                               int epilogue, int out_dtype, int* error, int act, float act_limit, float act_alpha,
+                               cudaStream_t stream);
+
 TS_API int ts_gemm_tcgen05(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
                            int epilogue, int out_dtype, int* error, cudaStream_t stream) {
+    return gemm_tcgen05_launch(W, x, y, M, N, K, ldx, ldy, epilogue, out_dtype, error, TS_ACT_SILU, 0.f, 1.f, stream);
+}
+
+// The gated epilogue with another activation than SiLU (TS_ACT_* of common.cuh): y[M, N/2], bfloat16.
+TS_API int ts_gemm_tcgen05_gated(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                                 int act, float limit, float alpha, int* error, cudaStream_t stream) {
+    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_CLAMPED_SWISH, "gemm_tcgen05: unknown activation %d", act);
+    return gemm_tcgen05_launch(W, x, y, M, N, K, ldx, ldy, EPI_SWIGLU, TS_BF16, error, act, limit, alpha, stream);
+}
+
+static int gemm_tcgen05_launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                               int epilogue, int out_dtype, int* error, int act, float act_limit, float act_alpha,
+                               cudaStream_t stream) {
     TS_REQUIRE(ts_gemm_tcgen05_supported(W, x, M, N, K, ldx), "gemm_tcgen05: sizes or alignment TMA does not take (M=%d N=%d K=%d)", M, N, K);
     TS_REQUIRE(error != nullptr, "gemm_tcgen05: an error word is needed");
     TS_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_SWIGLU, "gemm_tcgen05: unknown epilogue %d", epilogue);
@@ -607,7 +628,7 @@ TS_API int ts_gemm_tcgen05(const void* W, const void* x, void* y, int M, int N, 
     const int out_per_tile = epilogue == EPI_SWIGLU ? bn / 2 : bn;
     const int num_tiles = m_tiles * ((out_cols + out_per_tile - 1) / out_per_tile);
     CUtensorMap map_a, map_b;
-    GemmParams p{y, M, N, K, ldy, inter, out_dtype == TS_F32 ? 1 : 0, error};
+    GemmParams p{y, M, N, K, ldy, inter, out_dtype == TS_F32 ? 1 : 0, error, act, act_limit, act_alpha};
     // Two CTAs a tile of 256 x 256 where every pair of SMs gets at least six such tiles: measured on a B200, pairs were
     // 1 to 3 % faster than single CTAs from there on (Llama 3.2 1B's gate/up product at 2,048 and 8,192 rows, Llama
     // 3.1 8B's from 1,024 rows) and the same or slower with fewer tiles, whose last round leaves more pairs idle.

@@ -18,19 +18,7 @@
 //                    order of j, float32, rounded once.
 #include "common.cuh"
 
-__device__ __forceinline__ float gated_activation(int kind, float g, float u, float limit, float alpha);
-
-// kind 0: silu(g) * u;  1: relu(g) * u;  2: g' * sigmoid(alpha g') * (u' + 1) with g' = min(g, limit),
-// u' = clamp(u, -limit, limit)
-__device__ __forceinline__ float gated_activation(int kind, float g, float u, float limit, float alpha) {
-    if (kind == 1) return fmaxf(g, 0.f) * u;
-    if (kind == 2) {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        return g / (1.f + expf(-alpha * g)) * (u + 1.f);
-    }
-    return g / (1.f + expf(-g)) * u;
-}
+// the kinds of gated activation are those of common.cuh (ts_gated_activation)
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                  const int* __restrict__ seq_of_token, int* __restrict__ chosen, float* __restrict__ share,
@@ -198,7 +186,7 @@ moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __rest
         for (int j = 0; j < 4; ++j) {
             const int gc = col0 + tc + j;
             if (gc >= out_cols) continue;
-            const float v = GATED ? gated_activation(kind, acc[i][j], accu[i][j], limit, alpha) : acc[i][j];
+            const float v = GATED ? ts_gated_activation(kind, acc[i][j], accu[i][j], limit, alpha) : acc[i][j];
             dst[gc] = from_float<T>(v);
         }
     }
@@ -272,7 +260,7 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
             const float g = warp_sum(acc[r]);
             const float u = GATED ? warp_sum(accu[r]) : 0.f;
             if (lane == 0 && r < nrows)
-                y[(long long)(row0 + r) * out_cols + col] = from_float<T>(GATED ? gated_activation(kind, g, u, limit, alpha) : g);
+                y[(long long)(row0 + r) * out_cols + col] = from_float<T>(GATED ? ts_gated_activation(kind, g, u, limit, alpha) : g);
         }
     }
 }
@@ -361,7 +349,7 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
         const int i = (int)(idx % inter);
         const float g = to_float<T>(gate_up[t * 2 * inter + i]);
         const float u = to_float<T>(gate_up[t * 2 * inter + inter + i]);
-        out[idx] = from_float<T>(gated_activation(kind, g, u, limit, alpha));
+        out[idx] = from_float<T>(ts_gated_activation(kind, g, u, limit, alpha));
     }
 }
 

@@ -44,6 +44,8 @@ struct RopeArgs {
     __nv_bfloat16* v_pool;
     KVGeometry geo;
     int nh, nkv, hd, write_kv;
+    int act;                     // gated epilogue: the activation (TS_ACT_*), with its constants
+    float act_limit, act_alpha;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -230,8 +232,10 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
             if (row < rows_valid && token < M) {
                 // gate and up are materialised in bfloat16 by the reference before the activation
                 const float g = round_to<__nv_bfloat16>(gate), u = round_to<__nv_bfloat16>(up);
-                const float silu = round_to<__nv_bfloat16>(g / (1.f + expf(-g)));
-                store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 8 + row, silu * u);
+                float value;
+                if (rope.act == TS_ACT_SILU) value = round_to<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
+                else value = ts_gated_activation(rope.act, g, u, rope.act_limit, rope.act_alpha);
+                store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 8 + row, value);
             }
         }
     } else if (EPI == EPI_ROPE) {
@@ -353,6 +357,23 @@ TS_API int ts_skinny_linear(const void* W, const void* x, void* y, int M, int N,
     if (out_dtype == TS_BF16) return dispatch_warps<EPI_STORE, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     if (out_dtype == TS_F32) return dispatch_warps<EPI_STORE, float>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     return ts_fail("skinny_linear: unknown output dtype code %d", out_dtype);
+}
+
+// y[M, N/2] = act(x Wgate^T, x Wup^T) with another gated activation than SiLU in the epilogue (TS_ACT_* of common.cuh).
+TS_API int ts_skinny_linear_gated(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                                  int act, float limit, float alpha, cudaStream_t stream) {
+    TS_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 2 == 0, "skinny_linear_gated: bad sizes M=%d N=%d K=%d", M, N, K);
+    TS_REQUIRE(M <= ts_skinny_linear_max_rows(), "skinny_linear_gated: %d rows of x; the kernel takes up to %d", M,
+               ts_skinny_linear_max_rows());
+    TS_REQUIRE(K % 32 == 0 && ldx % 8 == 0 && ((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0),
+               "skinny_linear_gated: K a multiple of 32 and 16-byte aligned operands are needed");
+    TS_REQUIRE(act >= TS_ACT_SILU && act <= TS_ACT_CLAMPED_SWISH, "skinny_linear_gated: unknown activation %d", act);
+    if (M == 0) return 0;
+    RopeArgs args{};
+    args.act = act;
+    args.act_limit = limit;
+    args.act_alpha = alpha;
+    return dispatch_warps<EPI_SWIGLU, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, N / 2, stream, args);
 }
 
 // The q/k/v projection of a decode step with rotary embedding and the write into the paged cache in

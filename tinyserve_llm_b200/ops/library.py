@@ -48,6 +48,8 @@ _SIGNATURES = {
     "ts_skinny_linear_max_rows": ("int", ""),
     "ts_skinny_linear": ("int", "pppiiilliip"),
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
+    "ts_skinny_linear_gated": ("int", "pppiiilliffp"),
+    "ts_gemm_tcgen05_gated": ("int", "pppiiilliffpp"),
     "ts_stream_norm": ("int", "ppppppiifppifip"),
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
     "ts_head_norm_gate": ("int", "pplppiiifip"),
@@ -733,6 +735,36 @@ class Ops:
         """A few rows of bfloat16 x (a decode step): the engine's own weight-streaming kernel takes them."""
         return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.skinny_max_rows and x.shape[1] % 32 == 0
                 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def linear_gated(self, x: torch.Tensor, gate_up_weight: torch.Tensor, activation: str, limit: float = 0.0,
+                     alpha: float = 1.0) -> torch.Tensor:
+        """
+        act(x . Wgate^T, x . Wup^T) for the gated activations of `gated_activation`, [M, I], on the same products as
+        `linear_swiglu`: the weight-streaming kernel (a few rows) and the tcgen05 kernel (many rows) carry the
+        activation in their epilogue; in between, and in float32, the product and the activation kernel.
+        """
+        if activation == "silu":
+            return self.linear_swiglu(x, gate_up_weight)
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(gate_up_weight, "weight", x.dtype, 2)
+        if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1] or activation not in self.GATED_ACTIVATIONS:
+            raise KernelError("linear_gated: the weight must hold gate and up halves over x's columns; activation "
+                              f"{activation!r} of {sorted(self.GATED_ACTIVATIONS)}")
+        kind = self.GATED_ACTIVATIONS[activation]
+        M, K = x.shape
+        N = gate_up_weight.shape[0]
+        if self._skinny(x, gate_up_weight) and M <= self.swiglu_skinny_rows:
+            out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
+            self._call("ts_skinny_linear_gated", _ptr(gate_up_weight), _ptr(x), _ptr(out), M, N, K, K, N // 2, kind, limit,
+                       alpha, _stream())
+            return out
+        if x.dtype == torch.bfloat16 and M >= self.tcgen05_swiglu_min_rows and self.lib.ts_gemm_tcgen05_supported(
+                _ptr(gate_up_weight), _ptr(x), M, N, K, K):
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+            self._call("ts_gemm_tcgen05_gated", _ptr(gate_up_weight), _ptr(x), _ptr(out), M, N, K, K, N // 2, kind, limit,
+                       alpha, self.error_word().data_ptr(), _stream())
+            return out
+        return self.gated_activation(self.linear(x, gate_up_weight), activation, limit, alpha)
 
     def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
         """silu(x . Wgate^T) * (x . Wup^T) with Wgate, Wup the two halves of the weight's rows: [M, I]."""
