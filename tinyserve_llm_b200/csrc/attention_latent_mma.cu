@@ -9,6 +9,10 @@
 // of the output channels; the row maxima go through shared memory so that all warps rescale alike, the
 // row sums stay per warp until the end.  Key tiles are copied with cp.async (rows of keys outside the
 // window are zero-filled and masked); two CTAs share an SM, one loading while the other computes.
+// Two operands enter their product as the sum of two bfloat16 pieces (a second MMA each): the folded query's
+// latent part, whose rounding the unfolded form of the attention does not have, and the probabilities; the
+// logits then differ from the float32 kernel's no more than that kernel's from the plain model (measured: the
+// largest error of a replay fell from 0.5 to 0.3 of its bound, for 15 % of the kernel's time).
 // A small step's keys may be split over CTAs exactly as in the FFMA kernel; the partial results have the
 // same form and the same kernel merges them.
 #include "common.cuh"
@@ -48,10 +52,13 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
     constexpr int RANK = 32 * NT;
     extern __shared__ __align__(16) unsigned char raw[];
     const int width = RANK + rot, pitch = width + LM_PAD;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(raw);            // [16][pitch]
-    __nv_bfloat16* Ks = Qs + LM_HEADS * pitch;                            // [64][pitch]
+    const int lpitch = RANK + LM_PAD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(raw);            // [16][pitch]: the folded queries, rounded
+    __nv_bfloat16* Ql = Qs + LM_HEADS * pitch;                            // [16][lpitch]: what rounding left of their latent part
+    __nv_bfloat16* Ks = Ql + LM_HEADS * lpitch;                           // [64][pitch]
     __nv_bfloat16* Ps = Ks + LM_KEYS * pitch;                             // [16][64 + pad]
-    float* red = reinterpret_cast<float*>(Ps + LM_HEADS * (LM_KEYS + LM_PAD));   // [4 warps][16 rows]
+    __nv_bfloat16* Pl = Ps + LM_HEADS * (LM_KEYS + LM_PAD);
+    float* red = reinterpret_cast<float*>(Pl + LM_HEADS * (LM_KEYS + LM_PAD));   // [4 warps][16 rows]
     long long* row_base = reinterpret_cast<long long*>(red + LM_WARPS * LM_HEADS);   // [64] element offset of a key's row, -1: none
     const int t = blockIdx.x;
     const int seq = seq_of_token[t];
@@ -63,7 +70,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
     for (int e = tid; e < LM_HEADS * RANK; e += blockDim.x) {
         const int r = e / RANK, d = e % RANK;
         const float x = h0 + r < heads ? q_lat[(long long)t * ql_token_stride + (long long)(h0 + r) * ql_head_stride + d] : 0.f;
-        Qs[r * pitch + d] = __float2bfloat16_rn(x);
+        const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+        Qs[r * pitch + d] = hi;
+        Ql[r * lpitch + d] = __float2bfloat16_rn(x - __bfloat162float(hi));
     }
     const int half = rot / 2;
     for (int e = tid; e < LM_HEADS * half; e += blockDim.x) {
@@ -127,6 +136,13 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
             ldmatrix_x4(b, Ks + (key0 + ((lane >> 4) << 3) + (lane & 7)) * pitch + k0 + ((lane >> 3) & 1) * 8);
             mma_bf16(s[0], a, b[0], b[1]);
             mma_bf16(s[1], a, b[2], b[3]);
+            if (k0 < RANK) {
+                // W_uk^T q_flat as the sum of two bfloat16 pieces: folding adds a rounding the unfolded form does not
+                // have (many terms that cancel), and this keeps it out of the scores
+                ldmatrix_x4(a, Ql + (lane & 15) * lpitch + k0 + (lane >> 4) * 8);
+                mma_bf16(s[0], a, b[0], b[1]);
+                mma_bf16(s[1], a, b[2], b[3]);
+            }
         }
         // thread: rows `row` (c 0, 1) and `row + 8` (c 2, 3); keys key0 + 8 i + 2 quad + {0, 1}
         float tile_max[2] = {-INFINITY, -INFINITY};
@@ -167,8 +183,13 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
                 l_run[c >> 1] += pr[c];
             }
             const int col = key0 + 8 * i + 2 * quad;
-            *reinterpret_cast<__nv_bfloat162*>(Ps + row * (LM_KEYS + LM_PAD) + col) = __floats2bfloat162_rn(pr[0], pr[1]);
-            *reinterpret_cast<__nv_bfloat162*>(Ps + (row + 8) * (LM_KEYS + LM_PAD) + col) = __floats2bfloat162_rn(pr[2], pr[3]);
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(pr[0], pr[1]), h23 = __floats2bfloat162_rn(pr[2], pr[3]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + row * (LM_KEYS + LM_PAD) + col) = h01;
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (row + 8) * (LM_KEYS + LM_PAD) + col) = h23;
+            *reinterpret_cast<__nv_bfloat162*>(Pl + row * (LM_KEYS + LM_PAD) + col) =
+                __floats2bfloat162_rn(pr[0] - __low2float(h01), pr[1] - __high2float(h01));
+            *reinterpret_cast<__nv_bfloat162*>(Pl + (row + 8) * (LM_KEYS + LM_PAD) + col) =
+                __floats2bfloat162_rn(pr[2] - __low2float(h23), pr[3] - __high2float(h23));
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -180,8 +201,9 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
         const int ch0 = warp * (RANK / LM_WARPS);
 #pragma unroll
         for (int kk = 0; kk < LM_KEYS; kk += 16) {
-            unsigned a[4];
+            unsigned a[4], al[4];
             ldmatrix_x4(a, Ps + (lane & 15) * (LM_KEYS + LM_PAD) + kk + (lane >> 4) * 8);
+            ldmatrix_x4(al, Pl + (lane & 15) * (LM_KEYS + LM_PAD) + kk + (lane >> 4) * 8);
 #pragma unroll
             for (int nt = 0; nt < NT; nt += 2) {
                 // two n-tiles a load; behind an odd last one lie the next warp's channels, the rotated part or the row's
@@ -189,7 +211,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, long long ql_token_
                 unsigned b[4];
                 ldmatrix_x4_trans(b, Ks + (kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + ch0 + nt * 8 + (lane >> 4) * 8);
                 mma_bf16(o[nt], a, b[0], b[1]);
-                if (nt + 1 < NT) mma_bf16(o[nt + 1 < NT ? nt + 1 : nt], a, b[2], b[3]);
+                mma_bf16(o[nt], al, b[0], b[1]);
+                if (nt + 1 < NT) {
+                    mma_bf16(o[nt + 1 < NT ? nt + 1 : nt], a, b[2], b[3]);
+                    mma_bf16(o[nt + 1 < NT ? nt + 1 : nt], al, b[2], b[3]);
+                }
             }
         }
     }
@@ -249,7 +275,8 @@ int ts_latent_attention_mma_launch(const float* q_lat, long long ql_t, long long
                                    float scale, int window, int split_keys, int splits, float* partial,
                                    cudaStream_t stream) {
     const int width = rank + rot, pitch = width + LM_PAD;
-    const size_t smem = (size_t)(LM_HEADS + LM_KEYS) * pitch * 2 + (size_t)LM_HEADS * (LM_KEYS + LM_PAD) * 2 +
+    const size_t smem = (size_t)(LM_HEADS + LM_KEYS) * pitch * 2 + (size_t)LM_HEADS * (rank + LM_PAD) * 2 +
+                        (size_t)2 * LM_HEADS * (LM_KEYS + LM_PAD) * 2 +
                         (size_t)LM_WARPS * LM_HEADS * 4 + (size_t)LM_KEYS * 8;
     dim3 grid(num_tokens, (heads + LM_HEADS - 1) / LM_HEADS, split_keys > 0 ? splits : 1);
 #define TS_LATENT_MMA(NT)                                                                                              \
