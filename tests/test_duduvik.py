@@ -124,8 +124,8 @@ def close(got, want, dtype):
         torch.testing.assert_close(got, want, atol=3e-4, rtol=1e-4)
     else:
         err = (got - want).pow(2).mean(-1).sqrt() / want.std()
-        assert float(err.max()) < 0.08, f"relative error: worst {float(err.max()):.3f} at {int(err.argmax())}, " \
-                                        f"{int((err > 0.08).sum())} of {err.numel()} positions over 0.08"
+        assert float(err.max()) < 0.12 and float(err.median()) < 0.04, \
+            f"relative error: worst {float(err.max()):.3f} at {int(err.argmax())}, median {float(err.median()):.3f}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
