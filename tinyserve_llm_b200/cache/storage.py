@@ -34,6 +34,14 @@ class EntryBinding:
     group: int = 0
     state: torch.Tensor | None = None            # uint8 [slots, bytes of this entry's state]
     state_slots: torch.Tensor | None = None      # int32 [sequences] on the device, set per step
+    v_page_stride: int = -1   # the value pool's geometry where its head size differs from the keys' (-1: the same)
+    v_entry_offset: int = -1
+
+    def value_geometry(self) -> tuple[int, int]:
+        """(elements between pages, elements to this entry) of the value pool."""
+        if self.v_page_stride < 0:
+            return self.page_stride, self.entry_offset
+        return self.v_page_stride, self.v_entry_offset
 
 
 class DeviceCacheStorage:
@@ -49,7 +57,8 @@ class DeviceCacheStorage:
         for group, pages in zip(layout.groups, counts):
             shape = (pages, len(group.entries), group.num_kv_heads, layout.page_tokens, group.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device) if group.values else None)
+            v_shape = shape[:4] + (group.value_head_dim,)
+            self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=self.device) if group.values else None)
         self.state = None
         if layout.state_bytes:
             self.state = torch.zeros((max(num_state_slots, 1), layout.state_bytes), dtype=torch.uint8, device=self.device)
@@ -57,8 +66,8 @@ class DeviceCacheStorage:
     @staticmethod
     def bytes_per_page(layout: CacheLayout, dtype: torch.dtype) -> list[int]:
         """Keys and values of one page across the entries of each group."""
-        return [(2 if g.values else 1) * len(g.entries) * g.num_kv_heads * layout.page_tokens * g.head_dim * dtype.itemsize
-                for g in layout.groups]
+        return [len(g.entries) * g.num_kv_heads * layout.page_tokens * (g.head_dim + (g.value_head_dim if g.values else 0))
+                * dtype.itemsize for g in layout.groups]
 
     def entry_binding(self, entry: int) -> EntryBinding | None:
         """Geometry of a cache entry (block table and state rows are filled in per step)."""
@@ -71,6 +80,9 @@ class DeviceCacheStorage:
             per_entry = group.num_kv_heads * self.layout.page_tokens * group.head_dim
             binding = EntryBinding(self.k_pools[g], self.v_pools[g], per_entry * len(group.entries), per_entry * index,
                                    self.layout.page_tokens, self.num_pages[g], group=g)
+            if group.values and group.value_head_dim != group.head_dim:
+                per_entry_v = group.num_kv_heads * self.layout.page_tokens * group.value_head_dim
+                binding.v_page_stride, binding.v_entry_offset = per_entry_v * len(group.entries), per_entry_v * index
         offset = self.layout.state_offsets[entry] if entry < len(self.layout.state_offsets) else -1
         if offset >= 0:
             sizes = self.layout.state_sizes
@@ -83,7 +95,12 @@ class DeviceCacheStorage:
 
     # ------------------------------------------------------------------ what the manager asks for
     def copy_slots(self, group: int, src_page: int, dst_page: int, num_slots: int) -> None:
-        self.ops.copy_page_slots(self.k_pools[group], self.v_pools[group], src_page, dst_page, num_slots)
+        k_pool, v_pool = self.k_pools[group], self.v_pools[group]
+        if v_pool is not None and v_pool.shape != k_pool.shape:       # values of another head size: a copy of their own
+            self.ops.copy_page_slots(k_pool, None, src_page, dst_page, num_slots)
+            self.ops.copy_page_slots(v_pool, None, src_page, dst_page, num_slots)
+            return
+        self.ops.copy_page_slots(k_pool, v_pool, src_page, dst_page, num_slots)
 
     def copy_state(self, src_slot: int, dst_slot: int) -> None:
         self.state[dst_slot].copy_(self.state[src_slot])

@@ -65,16 +65,32 @@ class StreamRMSNormSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """
+    YaRN rescaling of rotary frequencies.  With turns(t) = dims ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(turns(fast)), 0), hi = min(ceil(turns(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1.
+    """
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class InlineRotarySpec(PartSpec):
     """
     Rotate-half rotation over the first `dims` channels of a head, channel i paired with i + dims/2,
     angle = position * base^(-2i/dims), computed in float32 inside the kernels (no position table,
-    so no longest position).
+    so no longest position).  `yarn` rescales the frequencies and magnifies cos and sin.
     """
 
     kind: str = field(init=False, default="rotary_inline")
     dims: int = 0
     base: float = 10000.0
+    yarn: YarnScaling | None = None
 
 
 @dataclass(frozen=True)
@@ -140,6 +156,114 @@ class AttentionSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class StreamLayerNormSpec(PartSpec):
+    """
+    Layer norm with a weight and no bias, (x - mean) / sqrt(mean((x - mean)^2) + eps) * w, beside a
+    residual stream kept in float32.  `weight_name` is the tensor's name behind the part's prefix.
+    """
+
+    kind: str = field(init=False, default="layernorm_stream")
+    size: int = 0
+    eps: float = 1e-6
+    weight_offset: float = 0.0
+    weight_name: str = "weight"
+
+
+@dataclass(frozen=True)
+class GatedAttentionSpec(PartSpec):
+    """
+    Causal grouped-query softmax attention whose keys and values may differ in head size, with
+    optional biases on q, k, v (tensor name + ".b"), an optional RMS norm of q and of k over the whole
+    projection (all heads at once, plain weights `q.norm`, `k.norm`) before the rotation, and an
+    optional output gate sigmoid(W_g h) on the concatenated heads before the output projection.
+    """
+
+    kind: str = field(init=False, default="gated_attention")
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    scale: float = 0.0
+    window: int = 0
+    bias: bool = False
+    qk_norm: bool = False
+    qk_norm_eps: float = 1e-6
+    output_gate: bool = False
+    position: PartSpec | None = None
+
+
+@dataclass(frozen=True)
+class GatedDeltaRuleSpec(PartSpec):
+    """
+    Gated delta rule over a matrix state per request and value head:
+    S <- diag(a_t) S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.
+    q, k (`num_kv_heads` heads) and v (`num_heads` heads) pass a short causal convolution of
+    `conv_taps` taps and silu; q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)),
+    q also times `q_scale`; beta = sigmoid(W_b h); a = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias))
+    per head and key channel; each head's o is RMS-normed (weight shared by the heads) and multiplied
+    by sigmoid(W_g2 W_g1 h).  The inner sizes of the two low-rank projections are the checkpoint's
+    (`decay_rank`, `gate_rank` only serve to draw random weights).
+    """
+
+    kind: str = field(init=False, default="gated_delta_rule")
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 1
+    q_scale: float = 1.0
+    unit_eps: float = 1e-6
+    out_norm_eps: float = 1e-6
+    decay_rank: int = 0
+    gate_rank: int = 0
+
+
+@dataclass(frozen=True)
+class MatrixLSTMSpec(PartSpec):
+    """
+    Matrix memory with exponential gating (mLSTM): per head a log input gate i = cap tanh((W_i h + b_i) / cap),
+    a log forget gate f = log_sigmoid(cap tanh((W_f h + b_f) / cap)), a running maximum m_t = max(f + m_(t-1), i)
+    that starts at 0, S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T, n_t likewise with k alone,
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + denominator_eps); each head's o is RMS-normed, the heads
+    concatenated, multiplied by a weight over all heads and by sigmoid(W_g h).
+    """
+
+    kind: str = field(init=False, default="mlstm")
+    hidden_size: int = 0
+    num_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    q_scale: float = 1.0
+    gate_cap: float = 15.0
+    denominator_eps: float = 1e-6
+    out_norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(PartSpec):
+    """
+    Mixers side by side on one input: sum_b scale_b * mixer_b(h).  `branches` holds (mixer description,
+    prefix of its tensors behind the mixer's own prefix, scale).  At most one branch keeps keys and values.
+    """
+
+    kind: str = field(init=False, default="parallel")
+    branches: tuple[tuple[PartSpec, str, float], ...] = ()
+
+
+@dataclass(frozen=True)
+class PlainMLPSpec(PartSpec):
+    """Ungated feed-forward down(act(up(x))); `activation` "relu2" is the square of relu."""
+
+    kind: str = field(init=False, default="plain_mlp")
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "relu2"
+    tensor_names: tuple[str, str] = ("up", "down")
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
     """Dense gated feed-forward: down(act(gate(x)) * up(x))."""
 
@@ -167,12 +291,16 @@ class RoutedExpertsSpec(PartSpec):
     hidden_size: int = 0
     num_experts: int = 0
     top: int = 1
-    expert: GatedMLPSpec | None = None
+    expert: GatedMLPSpec | PlainMLPSpec | None = None
     shared: GatedMLPSpec | None = None
     expert_prefix: str = "e{}."
     shared_prefix: str = "shared."
     router_name: str = "router"
     router_bias_name: str | None = "router.b"
+    # "softmax_chosen": softmax over the chosen logits; "sigmoid": each chosen expert's sigmoid(logit), not renormalised
+    scoring: str = "softmax_chosen"
+    # "output": the weight multiplies the expert's output; "input": its input (experts without a gate only)
+    weight_on: str = "output"
 
 
 @dataclass(frozen=True)
@@ -182,7 +310,7 @@ class BlockSpec:
     live under.  `arrangement` picks the wiring (the registry of arrangements); "pre_norm" is
     x + mixer(norm(x)) followed by x + ffn(norm(x)) with the adds deferred into the next norm;
     "sandwich_norm" norms each sublayer's output as well, x + norm_b(mixer(norm(x))), around a
-    float32 residual stream.
+    float32 residual stream; "pre_norm_stream" is "pre_norm" around a float32 residual stream.
     """
 
     arrangement: str

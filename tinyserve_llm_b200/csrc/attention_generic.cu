@@ -1,5 +1,6 @@
-// Paged causal grouped-query attention, generic version: any head size that is a multiple of 16 up
-// to 256, any number of heads and groups, any page size, float32 or bfloat16 storage.  One kernel
+// Paged causal grouped-query attention, generic version: any head size up to 256 (16-byte loads where
+// both head sizes are multiples of 16 bytes, element loads otherwise), values of another head size
+// than queries and keys, any number of heads and groups, any page size, float32 or bfloat16 storage.  One kernel
 // serves whole prompts, portions of prompts over a cached prefix, and single decoded tokens: the
 // step's keys are in the cache before it runs, and a query at position p sees keys max(0, p-w+1)..p
 // (w = window, 0 for all), which is the bottom-right-aligned causal rule of
@@ -38,12 +39,13 @@ __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, fl
 
 constexpr int WARPS = 4;
 
-template <typename T, int MAXHD>
+// queries: row t of `q` (`q_stride` elements a row), head h at h * hd; output [tokens, nh * vd]
+template <typename T, int MAXHD, bool VEC>
 __global__ void __launch_bounds__(WARPS * 32)
-paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T* __restrict__ k_pool,
-                               const T* __restrict__ v_pool, KVGeometry geo, const int* __restrict__ block_table,
-                               int table_width, const int* __restrict__ positions,
-                               const int* __restrict__ seq_of_token, int num_tokens, int nh, int nkv, int hd,
+paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out,
+                               const T* __restrict__ k_pool, const T* __restrict__ v_pool, KVGeometry geo, KVGeometry geo_v,
+                               const int* __restrict__ block_table, int table_width, const int* __restrict__ positions,
+                               const int* __restrict__ seq_of_token, int num_tokens, int nh, int nkv, int hd, int vd,
                                float scale, int window) {
     __shared__ float q_smem[WARPS][MAXHD];
     constexpr int VN = Vec16<T>::N;
@@ -52,12 +54,11 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
     if (item >= (long long)num_tokens * nh) return;
     const int t = (int)(item / nh), h = (int)(item % nh);
     const int seq = seq_of_token[t];
-    T* o_ptr = out + ((long long)t * nh + h) * hd;
+    T* o_ptr = out + ((long long)t * nh + h) * vd;
     if (seq < 0) return;                                      // padding row
     const int pos = positions[t];
     const int kvh = h / (nh / nkv);
-    const int row_width = (nh + 2 * nkv) * hd;
-    const T* q_ptr = qkv + (long long)t * row_width + (long long)h * hd;
+    const T* q_ptr = q + (long long)t * q_stride + (long long)h * hd;
     for (int d = lane; d < hd; d += 32) q_smem[warp][d] = to_float<T>(q_ptr[d]) * scale;
     __syncwarp();
 
@@ -68,6 +69,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const long long head_off = geo.entry_offset + (long long)kvh * geo.page_tokens * hd;
+    const long long head_off_v = geo_v.entry_offset + (long long)kvh * geo.page_tokens * vd;
     const int* table = block_table + (long long)seq * table_width;
     for (int j = lo + lane; j <= pos; j += 32) {
         const int page = table[j / geo.page_tokens];
@@ -75,14 +77,19 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
         const long long off = (long long)page * geo.page_stride + head_off + (long long)(j % geo.page_tokens) * hd;
         const T* kp = k_pool + off;
         float s = 0.f;
+        if (VEC) {
 #pragma unroll
-        for (int d0 = 0; d0 < MAXHD; d0 += VN) {
-            if (d0 < hd) {
-                float kv[VN];
-                load16<T>(kp + d0, kv);
+            for (int d0 = 0; d0 < MAXHD; d0 += VN) {
+                if (d0 < hd) {
+                    float kv[VN];
+                    load16<T>(kp + d0, kv);
 #pragma unroll
-                for (int e = 0; e < VN; ++e) s = fmaf(q_smem[warp][d0 + e], kv[e], s);
+                    for (int e = 0; e < VN; ++e) s = fmaf(q_smem[warp][d0 + e], kv[e], s);
+                }
             }
+        } else {
+#pragma unroll 4
+            for (int d = 0; d < hd; ++d) s = fmaf(q_smem[warp][d], to_float<T>(kp[d]), s);
         }
         if (s > m) {
             const float c = expf(m - s);                       // 0 on the first key (m = -inf)
@@ -93,15 +100,21 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
         }
         const float p = expf(s - m);
         l += p;
-        const T* vp = v_pool + off;
+        const T* vp = v_pool + (long long)page * geo_v.page_stride + head_off_v + (long long)(j % geo.page_tokens) * vd;
+        if (VEC) {
 #pragma unroll
-        for (int d0 = 0; d0 < MAXHD; d0 += VN) {
-            if (d0 < hd) {
-                float vv[VN];
-                load16<T>(vp + d0, vv);
+            for (int d0 = 0; d0 < MAXHD; d0 += VN) {
+                if (d0 < vd) {
+                    float vv[VN];
+                    load16<T>(vp + d0, vv);
 #pragma unroll
-                for (int e = 0; e < VN; ++e) o[d0 + e] = fmaf(p, vv[e], o[d0 + e]);
+                    for (int e = 0; e < VN; ++e) o[d0 + e] = fmaf(p, vv[e], o[d0 + e]);
+                }
             }
+        } else {
+#pragma unroll
+            for (int d = 0; d < MAXHD; ++d)
+                if (d < vd) o[d] = fmaf(p, to_float<T>(vp[d]), o[d]);
         }
     }
     // merge the lanes
@@ -111,7 +124,7 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
     const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
 #pragma unroll
     for (int d = 0; d < MAXHD; ++d) {
-        if (d < hd) {
+        if (d < vd) {
             const float total = warp_sum(o[d] * f);
             if (lane == (d & 31)) o_ptr[d] = from_float<T>(total * inv);
         }
@@ -119,41 +132,69 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, c
 }
 
 template <typename T, int MAXHD>
-static int launch(const void* qkv, void* out, const void* k_pool, const void* v_pool, KVGeometry geo,
-                  const int* block_table, int table_width, const int* positions, const int* seq_of_token,
-                  int num_tokens, int nh, int nkv, int hd, float scale, int window, cudaStream_t stream) {
+static int launch(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool, KVGeometry geo,
+                  KVGeometry geo_v, const int* block_table, int table_width, const int* positions,
+                  const int* seq_of_token, int num_tokens, int nh, int nkv, int hd, int vd, float scale, int window,
+                  cudaStream_t stream) {
     const long long items = (long long)num_tokens * nh;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
-    paged_attention_generic_kernel<T, MAXHD><<<blocks, WARPS * 32, 0, stream>>>(
-        (const T*)qkv, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, block_table, table_width, positions,
-        seq_of_token, num_tokens, nh, nkv, hd, scale, window);
+    const int vn = Vec16<T>::N;
+    // 16-byte loads need every row of keys and of values to start on a 16-byte boundary
+    const bool vec = hd % vn == 0 && vd % vn == 0 && geo.page_stride % vn == 0 && geo.entry_offset % vn == 0 &&
+                     geo_v.page_stride % vn == 0 && geo_v.entry_offset % vn == 0 && (uintptr_t)k_pool % 16 == 0 &&
+                     (uintptr_t)v_pool % 16 == 0;
+    if (vec)
+        paged_attention_generic_kernel<T, MAXHD, true><<<blocks, WARPS * 32, 0, stream>>>(
+            (const T*)q, q_stride, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, geo_v, block_table, table_width,
+            positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window);
+    else
+        paged_attention_generic_kernel<T, MAXHD, false><<<blocks, WARPS * 32, 0, stream>>>(
+            (const T*)q, q_stride, (T*)out, (const T*)k_pool, (const T*)v_pool, geo, geo_v, block_table, table_width,
+            positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window);
     TS_LAUNCH_CHECK("paged_attention_generic");
     return 0;
 }
 
+// Queries in a tensor of their own, values of head size `vd` in a pool with a geometry of its own.
+TS_API int ts_paged_attention_split(const void* q, long long q_stride, void* out, const void* k_pool, const void* v_pool,
+                                    long long page_stride, long long entry_offset, long long v_page_stride,
+                                    long long v_entry_offset, int page_tokens, int num_pages, const int* block_table,
+                                    int table_width, const int* positions, const int* seq_of_token, int num_tokens,
+                                    int nh, int nkv, int hd, int vd, float scale, int window, int dtype,
+                                    cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && nh > 0 && nkv > 0, "paged_attention: bad sizes");
+    TS_REQUIRE(nh % nkv == 0, "paged_attention: %d query heads are not a multiple of %d kv heads", nh, nkv);
+    TS_REQUIRE(hd > 0 && hd <= 256 && vd > 0 && vd <= 256,
+               "paged_attention: head sizes %d (keys) and %d (values) are not supported (up to 256)", hd, vd);
+    TS_REQUIRE(page_tokens > 0 && table_width > 0 && window >= 0, "paged_attention: bad page geometry");
+    if (num_tokens == 0) return 0;
+    KVGeometry geo{page_stride, entry_offset, page_tokens, num_pages};
+    KVGeometry geo_v{v_page_stride, v_entry_offset, page_tokens, num_pages};
+    const int widest = hd > vd ? hd : vd;
+#define TS_DISPATCH(TYPE)                                                                                          \
+    if (widest <= 32) return launch<TYPE, 32>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
+                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+    if (widest <= 64) return launch<TYPE, 64>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
+                                              positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+    if (widest <= 128) return launch<TYPE, 128>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, \
+                                                positions, seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream); \
+    return launch<TYPE, 256>(q, q_stride, out, k_pool, v_pool, geo, geo_v, block_table, table_width, positions,      \
+                             seq_of_token, num_tokens, nh, nkv, hd, vd, scale, window, stream);
+    if (dtype == TS_F32) { TS_DISPATCH(float) }
+    if (dtype == TS_BF16) { TS_DISPATCH(__nv_bfloat16) }
+#undef TS_DISPATCH
+    return ts_fail("paged_attention: unknown dtype code %d", dtype);
+}
+
+// Queries, keys and values of one head size in the columns [q | k | v] of one projection's output.
 TS_API int ts_paged_attention_generic(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                                       long long page_stride, long long entry_offset, int page_tokens, int num_pages,
                                       const int* block_table, int table_width, const int* positions,
                                       const int* seq_of_token, int num_tokens, int nh, int nkv, int hd, float scale,
                                       int window, int dtype, cudaStream_t stream) {
-    TS_REQUIRE(num_tokens >= 0 && nh > 0 && nkv > 0, "paged_attention: bad sizes");
-    TS_REQUIRE(nh % nkv == 0, "paged_attention: %d query heads are not a multiple of %d kv heads", nh, nkv);
     TS_REQUIRE(hd > 0 && hd % 16 == 0 && hd <= 256,
                "paged_attention: head_dim %d is not supported (multiples of 16 up to 256)", hd);
-    TS_REQUIRE(page_tokens > 0 && table_width > 0 && window >= 0, "paged_attention: bad page geometry");
-    if (num_tokens == 0) return 0;
-    KVGeometry geo{page_stride, entry_offset, page_tokens, num_pages};
-#define TS_DISPATCH(TYPE)                                                                                          \
-    if (hd <= 32) return launch<TYPE, 32>(qkv, out, k_pool, v_pool, geo, block_table, table_width, positions,       \
-                                          seq_of_token, num_tokens, nh, nkv, hd, scale, window, stream);             \
-    if (hd <= 64) return launch<TYPE, 64>(qkv, out, k_pool, v_pool, geo, block_table, table_width, positions,       \
-                                          seq_of_token, num_tokens, nh, nkv, hd, scale, window, stream);             \
-    if (hd <= 128) return launch<TYPE, 128>(qkv, out, k_pool, v_pool, geo, block_table, table_width, positions,     \
-                                            seq_of_token, num_tokens, nh, nkv, hd, scale, window, stream);           \
-    return launch<TYPE, 256>(qkv, out, k_pool, v_pool, geo, block_table, table_width, positions, seq_of_token,      \
-                             num_tokens, nh, nkv, hd, scale, window, stream);
-    if (dtype == TS_F32) { TS_DISPATCH(float) }
-    if (dtype == TS_BF16) { TS_DISPATCH(__nv_bfloat16) }
-#undef TS_DISPATCH
-    return ts_fail("paged_attention: unknown dtype code %d", dtype);
+    return ts_paged_attention_split(qkv, (long long)(nh + 2 * nkv) * hd, out, k_pool, v_pool, page_stride, entry_offset,
+                                    page_stride, entry_offset, page_tokens, num_pages, block_table, table_width,
+                                    positions, seq_of_token, num_tokens, nh, nkv, hd, hd, scale, window, dtype, stream);
 }

@@ -20,7 +20,16 @@
 // up in a fixed order after the tile.
 //
 // A second kernel norms each head's o over the value channels (with or without a weight),
-// multiplies by silu(gate) and rounds to the activation dtype for the output projection.
+// multiplies by silu(gate) or sigmoid(gate) and rounds to the activation dtype for the output projection.
+//
+// The scan also runs the delta rule (`beta` given):
+//   S <- diag(a_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+// where the read S^T k_t feeds back into the state, so the sixteen threads that share a column of S
+// are lanes of one warp and add up their shares with shuffles, token by token.
+// A value column past `v_cols` is the constant 1: with it the state carries the sum of the (decayed)
+// keys beside the matrix, and o's extra column is that sum's product with q (the normaliser of a
+// matrix memory with exponential gates).  The inputs of these variants are prepared by kernels of
+// their own, further down.
 #include "common.cuh"
 
 constexpr int LR_ROWGROUPS = 16;    // thread (r, j) holds rows r * MAXM .. r * MAXM + MAXM - 1 of column j of the state
@@ -65,14 +74,16 @@ __global__ void recurrence_prepare_kernel(const T* __restrict__ q, const T* __re
 
 struct RecurrenceArgs {
     const float* prepared; long long total;           // [3][tokens, heads * dim]: q, k, decay as they enter the recurrence
-    const void* v; long long v_stride;                // activation dtype, elements between tokens
+    const void* v; long long v_stride;                // elements between tokens; a head's values start at h * v_cols
+    int v_cols;                                       // value columns read from v; columns from here to vdim are 1
+    const float* beta;                                // [tokens, heads]: the delta rule's step size (null: plain recurrence)
     const int* cu_q; const int* slots;
     float* state; long long slot_stride;              // floats between slots; a slot holds [heads, dim, vdim]
     float* out;                                       // [tokens, heads * vdim] float32
     int heads, dim, vdim;
 };
 
-template <typename T, int MAXM>
+template <typename T, int MAXM, bool DELTA>
 __global__ void __launch_bounds__(LR_ROWGROUPS * LR_COLS)
 linear_recurrence_kernel(RecurrenceArgs p) {
     // staged rows are padded with zeros to LR_ROWGROUPS * MAXM channels: the inner loop needs no bound and reads
@@ -85,11 +96,15 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     float* a_s = k_s + LR_TILE * PITCH;
     float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][LR_COLS]
     float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
+    float* b_s = part + LR_TILE * LR_ROWGROUPS * LR_COLS; // [LR_TILE] (delta rule)
     const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
     const int slot = p.slots[seq];
     const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
     if (slot < 0 || end <= begin) return;                // a padding request, or one that feeds nothing
-    const int r = threadIdx.x / LR_COLS, jj = threadIdx.x % LR_COLS, j = j0 + jj;
+    // plain: the threads of a row group are neighbours (their loads of a state row coalesce); delta rule: the
+    // sixteen row groups of a column are the lanes of half a warp
+    const int r = DELTA ? threadIdx.x % LR_ROWGROUPS : threadIdx.x / LR_COLS;
+    const int jj = DELTA ? threadIdx.x / LR_ROWGROUPS : threadIdx.x % LR_COLS, j = j0 + jj;
     const bool live = j < vdim;
     float* st = p.state + (long long)slot * p.slot_stride + (long long)h * dim * vdim;
     float S[MAXM];
@@ -105,6 +120,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     constexpr int ROUNDS = LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS);
     float raw_q[ROUNDS], raw_k[ROUNDS], raw_a[ROUNDS];
     T raw_v;                                             // as loaded: converting would wait for the load
+    float raw_b = 0.f;
     auto fetch = [&](int t0, int n) {
 #pragma unroll
         for (int round = 0; round < ROUNDS; ++round) {
@@ -119,8 +135,9 @@ linear_recurrence_kernel(RecurrenceArgs p) {
             }
         }
         const int tt = threadIdx.x / LR_COLS, c = threadIdx.x % LR_COLS;       // LR_TILE * LR_COLS = one value a thread
-        raw_v = from_float<T>(0.f);
-        if (tt < n && j0 + c < vdim) raw_v = v[(long long)(t0 + tt) * p.v_stride + (long long)h * vdim + j0 + c];
+        raw_v = from_float<T>(j0 + c >= p.v_cols && j0 + c < vdim ? 1.f : 0.f);
+        if (tt < n && j0 + c < p.v_cols) raw_v = v[(long long)(t0 + tt) * p.v_stride + (long long)h * p.v_cols + j0 + c];
+        if (DELTA && threadIdx.x < LR_TILE) raw_b = threadIdx.x < n ? p.beta[(long long)(t0 + threadIdx.x) * p.heads + h] : 0.f;
     };
     fetch(begin, min(LR_TILE, end - begin));
     for (int t0 = begin; t0 < end; t0 += LR_TILE) {
@@ -134,6 +151,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
             a_s[e] = raw_a[round];
         }
         v_s[threadIdx.x] = to_float<T>(raw_v);
+        if (DELTA && threadIdx.x < LR_TILE) b_s[threadIdx.x] = raw_b;
         if (t0 + LR_TILE < end) fetch(t0 + LR_TILE, min(LR_TILE, end - t0 - LR_TILE));   // under way during this tile's work
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
@@ -142,15 +160,46 @@ linear_recurrence_kernel(RecurrenceArgs p) {
             const float4* kt = reinterpret_cast<const float4*>(k_s + tt * PITCH + r * MAXM);
             const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + r * MAXM);
             float acc = 0.f;
+            if (DELTA) {
+                float kreg[MAXM];
+                float read = 0.f;
 #pragma unroll
-            for (int m4 = 0; m4 < MAXM / 4; ++m4) {
-                const float4 q4 = qt[m4], k4 = kt[m4], a4 = at[m4];
-                const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) {
+                    const float4 k4 = kt[m4], a4 = at[m4];
+                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int m = 4 * m4 + c;
-                    S[m] = fmaf(aa[c], S[m], kk[c] * vj);
-                    acc = fmaf(S[m], qq[c], acc);
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = 4 * m4 + c;
+                        kreg[m] = kk[c];
+                        S[m] *= aa[c];
+                        read = fmaf(S[m], kk[c], read);
+                    }
+                }
+#pragma unroll
+                for (int o = LR_ROWGROUPS / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+                const float u = b_s[tt] * (vj - read);
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) {
+                    const float4 q4 = qt[m4];
+                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = 4 * m4 + c;
+                        S[m] = fmaf(kreg[m], u, S[m]);
+                        acc = fmaf(S[m], qq[c], acc);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) {
+                    const float4 q4 = qt[m4], k4 = kt[m4], a4 = at[m4];
+                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = 4 * m4 + c;
+                        S[m] = fmaf(aa[c], S[m], kk[c] * vj);
+                        acc = fmaf(S[m], qq[c], acc);
+                    }
                 }
             }
             part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
@@ -175,21 +224,48 @@ linear_recurrence_kernel(RecurrenceArgs p) {
 template <typename T>
 static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t stream) {
     dim3 grid((p.vdim + LR_COLS - 1) / LR_COLS, p.heads, num_seqs);
-#define TS_RECURRENCE(MAXM)                                                                                        \
+#define TS_RECURRENCE(MAXM, DELTA)                                                                                 \
     do {                                                                                                           \
         const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * LR_COLS +                       \
-                                     LR_TILE * LR_ROWGROUPS * LR_COLS) * sizeof(float);                            \
+                                     LR_TILE * LR_ROWGROUPS * LR_COLS + LR_TILE) * sizeof(float);                  \
         if (smem > 48 * 1024)                                                                                      \
-            cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+            cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                                       \
-        linear_recurrence_kernel<T, MAXM><<<grid, LR_ROWGROUPS * LR_COLS, smem, stream>>>(p);                      \
+        linear_recurrence_kernel<T, MAXM, DELTA><<<grid, LR_ROWGROUPS * LR_COLS, smem, stream>>>(p);               \
     } while (0)
-    if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4);
-    else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8);
-    else TS_RECURRENCE(16);
+    if (p.beta) {
+        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, true);
+        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, true);
+        else TS_RECURRENCE(16, true);
+    } else {
+        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, false);
+        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, false);
+        else TS_RECURRENCE(16, false);
+    }
 #undef TS_RECURRENCE
     TS_LAUNCH_CHECK("linear_recurrence");
     return 0;
+}
+
+// The scan alone, from inputs a kernel of the caller's prepared: prepared [3][tokens, heads * dim] float32
+// (q, k and the decay as they enter the recurrence), v [tokens, heads * v_cols] in float32 or the activation
+// dtype, beta [tokens, heads] or null.  A slot holds [heads, dim, vdim] floats.
+TS_API int ts_recurrence_scan(const float* prepared, const void* v, long long v_stride, int v_cols, int v_dtype,
+                              const float* beta, const int* cu_q, const int* slots, int num_seqs, float* state,
+                              long long slot_stride, float* out, int heads, int dim, int vdim, int num_tokens,
+                              cudaStream_t stream) {
+    TS_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && num_seqs >= 0 && num_tokens >= 0, "recurrence_scan: bad sizes");
+    TS_REQUIRE(dim <= 16 * LR_ROWGROUPS, "recurrence_scan: %d key channels a head are not supported (up to %d)", dim,
+               16 * LR_ROWGROUPS);
+    TS_REQUIRE(v_cols >= 0 && v_cols <= vdim, "recurrence_scan: %d of %d value columns", v_cols, vdim);
+    TS_REQUIRE(slot_stride >= (long long)heads * dim * vdim, "recurrence_scan: a state slot is too small");
+    TS_REQUIRE(num_seqs <= 65535 && heads <= 65535, "recurrence_scan: grid too large");
+    if (num_seqs == 0 || num_tokens == 0) return 0;
+    const long long total = (long long)num_tokens * heads * dim;
+    RecurrenceArgs p{prepared, total, v, v_stride, v_cols, beta, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
+    if (v_dtype == TS_F32) return launch_recurrence<float>(p, num_seqs, stream);
+    if (v_dtype == TS_BF16) return launch_recurrence<__nv_bfloat16>(p, num_seqs, stream);
+    return ts_fail("recurrence_scan: unknown dtype code %d", v_dtype);
 }
 
 TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
@@ -221,47 +297,58 @@ TS_API int ts_linear_recurrence(const void* q, const void* k, const void* v, lon
     else
         return ts_fail("linear_recurrence: unknown dtype code %d", dtype);
     TS_LAUNCH_CHECK("linear_recurrence (prepare)");
-    RecurrenceArgs p{prepared, total, v, v_stride, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
+    RecurrenceArgs p{prepared, total, v, v_stride, vdim, nullptr, cu_q, slots, state, slot_stride, out, heads, dim, vdim};
     if (dtype == TS_F32) return launch_recurrence<float>(p, num_seqs, stream);
     return launch_recurrence<__nv_bfloat16>(p, num_seqs, stream);
 }
 
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); one warp a (token, head).
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]) * scale; one warp a
+// (token, head).  `gate_kind` 0: silu, 1: sigmoid.  The weight is shared by the heads (`weight_stride` 0) or one
+// stretch a head (`weight_stride` = vdim).  A head of o is `o_head` floats apart from the next (vdim, or more where
+// o carries extra columns).  With `log_max` ([tokens, heads]) the head is first divided by
+// max(|o[t, h, vdim]|, exp(-log_max[t, h])) + 1e-6: the normaliser of a matrix memory with exponential gates, whose
+// product with q the scan left in column vdim.  The result may be a column stretch of a wider tensor (`out_stride`).
 template <typename T>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
-                                      const float* __restrict__ weight, T* __restrict__ out, long long items, int heads,
-                                      int vdim, float eps) {
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, int o_head, const T* __restrict__ gate,
+                                      long long gate_stride, const float* __restrict__ weight, int weight_stride,
+                                      const float* __restrict__ log_max, T* __restrict__ out, long long out_stride,
+                                      long long items, int heads, int vdim, float eps, int gate_kind, float scale) {
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= items) return;
     const int lane = threadIdx.x & 31;
     const long long t = item / heads;
     const int h = (int)(item % heads);
-    const float* orow = o + item * vdim;
+    const float* orow = o + item * o_head;
+    float pre = 1.f;
+    if (log_max) pre = 1.f / (fmaxf(fabsf(orow[vdim]), expf(-log_max[item])) + 1e-6f);
     float acc = 0.f;
-    for (int j = lane; j < vdim; j += 32) acc += orow[j] * orow[j];
+    for (int j = lane; j < vdim; j += 32) acc += (orow[j] * pre) * (orow[j] * pre);
     const float inv = 1.f / sqrtf(warp_sum(acc) / (float)vdim + eps);
     const T* g = gate + t * gate_stride + (long long)h * vdim;
-    T* dst = out + item * vdim;
+    T* dst = out + t * out_stride + (long long)h * vdim;
+    const float* w = weight ? weight + (long long)h * weight_stride : nullptr;
     for (int j = lane; j < vdim; j += 32) {
         const float x = to_float<T>(g[j]);
-        const float silu = x / (1.f + expf(-x));
-        const float w = weight ? weight[j] : 1.f;
-        dst[j] = from_float<T>(orow[j] * inv * w * silu);
+        const float sig = 1.f / (1.f + expf(-x));
+        const float act = gate_kind == 1 ? sig : x * sig;
+        dst[j] = from_float<T>(orow[j] * pre * inv * (w ? w[j] : 1.f) * act * scale);
     }
 }
 
-TS_API int ts_head_norm_gate(const float* o, const void* gate, long long gate_stride, const float* weight, void* out,
-                             int num_tokens, int heads, int vdim, float eps, int dtype, cudaStream_t stream) {
-    TS_REQUIRE(num_tokens >= 0 && heads > 0 && vdim > 0, "head_norm_gate: bad sizes");
+TS_API int ts_head_norm_gate(const float* o, int o_head, const void* gate, long long gate_stride, const float* weight,
+                             int weight_stride, const float* log_max, void* out, long long out_stride, int num_tokens,
+                             int heads, int vdim, float eps, int gate_kind, float scale, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && heads > 0 && vdim > 0 && o_head >= vdim, "head_norm_gate: bad sizes");
+    TS_REQUIRE(!log_max || o_head > vdim, "head_norm_gate: the normaliser's column is missing");
     if (num_tokens == 0) return 0;
     const long long items = (long long)num_tokens * heads;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     if (dtype == TS_F32)
-        head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, gate_stride, weight, (float*)out,
-                                                                 items, heads, vdim, eps);
+        head_norm_gate_kernel<float><<<blocks, 128, 0, stream>>>(o, o_head, (const float*)gate, gate_stride, weight,
+            weight_stride, log_max, (float*)out, out_stride, items, heads, vdim, eps, gate_kind, scale);
     else if (dtype == TS_BF16)
-        head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, gate_stride, weight,
-                                                                         (__nv_bfloat16*)out, items, heads, vdim, eps);
+        head_norm_gate_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, o_head, (const __nv_bfloat16*)gate, gate_stride,
+            weight, weight_stride, log_max, (__nv_bfloat16*)out, out_stride, items, heads, vdim, eps, gate_kind, scale);
     else
         return ts_fail("head_norm_gate: unknown dtype code %d", dtype);
     TS_LAUNCH_CHECK("head_norm_gate");

@@ -2,7 +2,8 @@
 // feed-forward layers, and the outputs are added with the softmax of the chosen logits as weights.
 //
 //   ts_moe_route     per token: the `top` largest router logits (float32, bias added here; ties go to
-//                    the lower index), their softmax, and a count per expert.
+//                    the lower index), their softmax, and a count per expert.  `scoring` 1: a chosen
+//                    expert's share is sigmoid(logit) instead, not renormalised.
 //   ts_moe_arrange   (token, choice) pairs sorted by expert: every CTA takes the exclusive scan of the
 //                    counts and places its pairs behind their expert's offset.  Which row of an
 //                    expert's stretch a pair lands in is not fixed; no result depends on it.
@@ -10,19 +11,21 @@
 //                    W [experts, N, K].  Tiles of 32 pairs x 64 columns, FFMA with float32 sums over k
 //                    in ascending order (a pair's result does not depend on its row or on the batch).
 //                    With `gated`, W_e holds gate rows then up rows and the epilogue applies the gated
-//                    activation (the kinds are listed below) before it stores.  Input rows are
+//                    activation (the kinds are listed below) before it stores.  Without `gated`, `unary` 1
+//                    stores relu(s)^2 and `row_scale` (one factor a pair) multiplies the sum first: an
+//                    expert whose input is weighted, since W (c x) = c (W x).  Input rows are
 //                    gathered by token for the first product; the second reads the sorted rows.
 //                    A step of up to 64 pairs takes a weight-streaming kernel instead (further down); large
 //                    bfloat16 steps may be given to the library's grouped product by the caller.
 //   ts_moe_combine   out[t] = sum_j share[t, j] * y[row of (t, j)] (+ the shared expert's output), in the
-//                    order of j, float32, rounded once.
+//                    order of j, float32, rounded once.  Without `share` every weight is 1.
 #include "common.cuh"
 
 // the kinds of gated activation are those of common.cuh (ts_gated_activation)
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                  const int* __restrict__ seq_of_token, int* __restrict__ chosen, float* __restrict__ share,
-                                 int* __restrict__ counts, int num_tokens, int experts, int top) {
+                                 int* __restrict__ counts, int num_tokens, int experts, int top, int scoring) {
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= num_tokens) return;
     const int lane = threadIdx.x & 31;
@@ -49,7 +52,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
         }
         if (arg != 0x7fffffff && (arg & 31) == lane) taken_lo |= 1ull << (arg >> 5);
         if (j == 0) first = best;
-        const float w = expf(best - first);                // the first choice is the largest
+        const float w = scoring == 1 ? 1.f / (1.f + expf(-best)) : expf(best - first);   // the first choice is the largest
         total += w;
         if (lane == 0) {
             chosen[(long long)t * top + j] = arg;
@@ -58,17 +61,17 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
         }
     }
     __syncwarp();
-    if (lane == 0)
+    if (lane == 0 && scoring == 0)
         for (int j = 0; j < top; ++j) share[(long long)t * top + j] /= total;
 }
 
 TS_API int ts_moe_route(const float* logits, const float* bias, const int* seq_of_token, int* chosen, float* share,
-                        int* counts, int num_tokens, int experts, int top, cudaStream_t stream) {
+                        int* counts, int num_tokens, int experts, int top, int scoring, cudaStream_t stream) {
     TS_REQUIRE(experts > 0 && top > 0 && top <= experts, "moe_route: %d of %d experts", top, experts);
     TS_REQUIRE(experts <= 2048, "moe_route: %d experts are not supported (up to 2048)", experts);
     if (num_tokens <= 0) return 0;
     moe_route_kernel<<<(num_tokens + 3) / 4, 128, 0, stream>>>(logits, bias, seq_of_token, chosen, share, counts,
-                                                               num_tokens, experts, top);
+                                                               num_tokens, experts, top, scoring);
     TS_LAUNCH_CHECK("moe_route");
     return 0;
 }
@@ -111,7 +114,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ pair_of_row, int top,
                   const int* __restrict__ offsets, int experts, const T* __restrict__ w, int N, int K, T* __restrict__ y,
-                  int out_cols, int kind, float limit, float alpha) {
+                  int out_cols, int kind, float limit, float alpha, const float* __restrict__ row_scale, int unary) {
     __shared__ float As[GK][GM + 1];
     __shared__ float Bs[GK][GN + 1];
     __shared__ float Us[GATED ? GK : 1][GN + 1];
@@ -129,10 +132,17 @@ moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __rest
     const int nrows = min(GM, last - row0);
     const int col0 = blockIdx.x * GN;
     const int tid = threadIdx.x;
+    __shared__ float rows_scale[GM];
     if (tid < GM) {
         int src = -1;
-        if (tid < nrows) src = pair_of_row ? pair_of_row[row0 + tid] / top : row0 + tid;
+        float c = 1.f;
+        if (tid < nrows) {
+            const int pair = pair_of_row ? pair_of_row[row0 + tid] : row0 + tid;
+            src = pair_of_row ? pair / top : pair;
+            if (row_scale) c = row_scale[pair];
+        }
         rows_src[tid] = src;
+        rows_scale[tid] = c;
     }
     __syncthreads();
     const T* we = w + (long long)e * N * K;
@@ -186,7 +196,8 @@ moe_linear_kernel(const T* __restrict__ x, long long x_stride, const int* __rest
         for (int j = 0; j < 4; ++j) {
             const int gc = col0 + tc + j;
             if (gc >= out_cols) continue;
-            const float v = GATED ? ts_gated_activation(kind, acc[i][j], accu[i][j], limit, alpha) : acc[i][j];
+            float v = GATED ? ts_gated_activation(kind, acc[i][j], accu[i][j], limit, alpha) : acc[i][j] * rows_scale[tr + i];
+            if (!GATED && unary == 1) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
             dst[gc] = from_float<T>(v);
         }
     }
@@ -201,8 +212,10 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(SWARPS * 32)
 moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ pair_of_row, int top,
                        const int* __restrict__ offsets, int experts, const T* __restrict__ w, int N, int K,
-                       T* __restrict__ y, int out_cols, int cols_per_cta, int kind, float limit, float alpha) {
+                       T* __restrict__ y, int out_cols, int cols_per_cta, int kind, float limit, float alpha,
+                       const float* __restrict__ row_scale, int unary) {
     extern __shared__ __align__(16) unsigned char raw[];
+    __shared__ float rows_scale[SR];
     T* xs = reinterpret_cast<T*>(raw);                    // [SR][K]
     constexpr int VN = 16 / sizeof(T);
     int tile = blockIdx.y, e = 0, first = 0, last = 0;
@@ -223,6 +236,11 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
             v = *reinterpret_cast<const uint4*>(x + (long long)src * x_stride + c * VN);
         }
         *reinterpret_cast<uint4*>(xs + (long long)r * K + c * VN) = v;
+    }
+    if (threadIdx.x < SR) {
+        float c = 1.f;
+        if (row_scale && (int)threadIdx.x < nrows) c = row_scale[pair_of_row ? pair_of_row[row0 + threadIdx.x] : row0 + threadIdx.x];
+        rows_scale[threadIdx.x] = c;
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -259,16 +277,20 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
         for (int r = 0; r < SR; ++r) {
             const float g = warp_sum(acc[r]);
             const float u = GATED ? warp_sum(accu[r]) : 0.f;
-            if (lane == 0 && r < nrows)
-                y[(long long)(row0 + r) * out_cols + col] = from_float<T>(GATED ? ts_gated_activation(kind, g, u, limit, alpha) : g);
+            if (lane == 0 && r < nrows) {
+                float v = GATED ? ts_gated_activation(kind, g, u, limit, alpha) : g * rows_scale[r];
+                if (!GATED && unary == 1) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
+                y[(long long)(row0 + r) * out_cols + col] = from_float<T>(v);
+            }
         }
     }
 }
 
 TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_row, int top, const int* offsets,
                          int experts, const void* w, int N, int K, void* y, int pairs, int gated, int kind, float limit,
-                         float alpha, int dtype, cudaStream_t stream) {
+                         float alpha, const float* row_scale, int unary, int dtype, cudaStream_t stream) {
     TS_REQUIRE(experts > 0 && N > 0 && K > 0 && top > 0, "moe_linear: bad sizes");
+    TS_REQUIRE(!gated || (!row_scale && !unary), "moe_linear: a gated product takes no row scale and no other activation");
     TS_REQUIRE(!gated || N % 2 == 0, "moe_linear: a gated weight holds gate and up rows of equal number");
     if (pairs <= 0) return 0;
     const int out_cols = gated ? N / 2 : N;
@@ -286,7 +308,7 @@ TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_r
                                      (int)smem);                                                                       \
             moe_linear_rows_kernel<TYPE, G><<<sgrid, SWARPS * 32, smem, stream>>>(                                     \
                 (const TYPE*)x, x_stride, pair_of_row, top, offsets, experts, (const TYPE*)w, N, K, (TYPE*)y, out_cols, \
-                cols_per_cta, kind, limit, alpha);                                                                     \
+                cols_per_cta, kind, limit, alpha, row_scale, unary);                                                                  \
         } while (0)
         if (dtype == TS_F32) { if (gated) TS_MOE_ROWS(float, true); else TS_MOE_ROWS(float, false); }
         else { if (gated) TS_MOE_ROWS(__nv_bfloat16, true); else TS_MOE_ROWS(__nv_bfloat16, false); }
@@ -299,7 +321,8 @@ TS_API int ts_moe_linear(const void* x, long long x_stride, const int* pair_of_r
     dim3 grid((out_cols + GN - 1) / GN, row_tiles);
 #define TS_MOE_LINEAR(TYPE, G)                                                                                       \
     moe_linear_kernel<TYPE, G><<<grid, 256, 0, stream>>>((const TYPE*)x, x_stride, pair_of_row, top, offsets, experts, \
-                                                         (const TYPE*)w, N, K, (TYPE*)y, out_cols, kind, limit, alpha)
+                                                         (const TYPE*)w, N, K, (TYPE*)y, out_cols, kind, limit, alpha, \
+                                                         row_scale, unary)
     if (dtype == TS_F32) { if (gated) TS_MOE_LINEAR(float, true); else TS_MOE_LINEAR(float, false); }
     else if (dtype == TS_BF16) { if (gated) TS_MOE_LINEAR(__nv_bfloat16, true); else TS_MOE_LINEAR(__nv_bfloat16, false); }
     else return ts_fail("moe_linear: unknown dtype code %d", dtype);
@@ -317,7 +340,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
         float s = 0.f;
         for (int j = 0; j < top; ++j) {
             const int row = row_of_pair[t * top + j];
-            if (row >= 0) s = fmaf(share[t * top + j], to_float<T>(y[(long long)row * width + i]), s);
+            if (row >= 0) s = fmaf(share ? share[t * top + j] : 1.f, to_float<T>(y[(long long)row * width + i]), s);
         }
         if (shared_out) s += to_float<T>(shared_out[t * width + i]);
         out[t * width + i] = from_float<T>(s);
@@ -368,5 +391,38 @@ TS_API int ts_gated_activation(const void* gate_up, void* out, int num_tokens, i
     else
         return ts_fail("gated_activation: unknown dtype code %d", dtype);
     TS_LAUNCH_CHECK("gated_activation");
+    return 0;
+}
+
+// out[r, c] = act(x[r, c] * scale[pair of sorted row r]) for the ungated activations (after a library product).
+template <typename T>
+__global__ void row_scaled_activation_kernel(const T* __restrict__ x, const int* __restrict__ pair_of_row,
+                                             const float* __restrict__ row_scale, T* __restrict__ out, long long total,
+                                             int cols, int unary) {
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / cols;
+        float v = to_float<T>(x[idx]);
+        if (row_scale) v *= row_scale[pair_of_row ? pair_of_row[r] : r];
+        if (unary == 1) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
+        out[idx] = from_float<T>(v);
+    }
+}
+
+TS_API int ts_row_scaled_activation(const void* x, const int* pair_of_row, const float* row_scale, void* out, int rows,
+                                    int cols, int unary, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(rows >= 0 && cols > 0, "row_scaled_activation: bad sizes");
+    if (rows == 0) return 0;
+    const long long total = (long long)rows * cols;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == TS_F32)
+        row_scaled_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, pair_of_row, row_scale, (float*)out,
+                                                                        total, cols, unary);
+    else if (dtype == TS_BF16)
+        row_scaled_activation_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, pair_of_row, row_scale,
+                                                                                (__nv_bfloat16*)out, total, cols, unary);
+    else
+        return ts_fail("row_scaled_activation: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("row_scaled_activation");
     return 0;
 }

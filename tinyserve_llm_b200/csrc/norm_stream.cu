@@ -10,13 +10,20 @@
 // wanted places), `ids` (the row is table[ids[r]] * scale and starts the stream: the embedding).
 // Statistics, weights, the sum and the stream are float32; the branch and `out` have the activation
 // dtype.  The weights are given as they multiply (an offset of the stored weight is added by the host).
+//
+// `flags`: TS_NORM_CENTERED makes the opening norm a layer norm without bias,
+//   opening(s) = (s - mean(s)) / sqrt(mean((s - mean(s))^2) + eps) * w_open;
+// TS_NORM_PLAIN_ADD adds the branch as it is (a block that norms only the inputs of its sublayers).
 #include "common.cuh"
+
+enum { TS_NORM_CENTERED = 1, TS_NORM_PLAIN_ADD = 2 };
 
 template <typename T>
 __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __restrict__ w_close, float* stream,
                                    const float* __restrict__ w_open, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps, const T* __restrict__ table,
-                                   const int* __restrict__ ids, int table_rows, float scale, int write_stream) {
+                                   const int* __restrict__ ids, int table_rows, float scale, int write_stream,
+                                   int flags) {
     extern __shared__ float row[];                // width floats, then 32 of scratch
     float* scratch = row + width;
     const int r = blockIdx.x;
@@ -28,6 +35,9 @@ __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __
         const bool zeros = id < 0 || id >= table_rows;
         const T* tr = table + (long long)(zeros ? 0 : id) * width;
         for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = zeros ? 0.f : to_float<T>(tr[i]) * scale;
+    } else if (branch && (flags & TS_NORM_PLAIN_ADD)) {
+        const T* br = branch + (long long)src * width;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = sr[i] + to_float<T>(br[i]);
     } else if (branch) {
         const T* br = branch + (long long)src * width;
         float acc = 0.f;
@@ -45,19 +55,26 @@ __global__ void stream_norm_kernel(const T* __restrict__ branch, const float* __
     if (write_stream && (ids || branch))
         for (int i = threadIdx.x; i < width; i += blockDim.x) sr[i] = row[i];
     if (!w_open) return;
+    float mean = 0.f;
+    if (flags & TS_NORM_CENTERED) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+        mean = block_sum(sum, scratch) / (float)width;
+        __syncthreads();                          // scratch is used again below
+    }
     float acc = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) acc += row[i] * row[i];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) acc += (row[i] - mean) * (row[i] - mean);
     const float inv = 1.f / sqrtf(block_sum(acc, scratch) / (float)width + eps);
     T* o = out + (long long)r * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>(row[i] * inv * w_open[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_float<T>((row[i] - mean) * inv * w_open[i]);
 }
 
 TS_API int ts_stream_norm(const void* branch, const float* w_close, float* stream, const float* w_open, void* out,
                           const int* rows, int count, int width, float eps, const void* table, const int* ids,
-                          int table_rows, float scale, int dtype, cudaStream_t stream_handle) {
+                          int table_rows, float scale, int flags, int dtype, cudaStream_t stream_handle) {
     TS_REQUIRE(count >= 0 && width > 0, "stream_norm: bad sizes rows=%d width=%d", count, width);
     TS_REQUIRE(stream != nullptr, "stream_norm: no residual stream");
-    TS_REQUIRE(!(branch && !w_close), "stream_norm: a branch needs the weight of its closing norm");
+    TS_REQUIRE(!(branch && !w_close && !(flags & TS_NORM_PLAIN_ADD)), "stream_norm: a branch needs the weight of its closing norm");
     TS_REQUIRE(!(w_open && !out), "stream_norm: an opening norm needs an output");
     TS_REQUIRE(!(ids && (!table || branch)), "stream_norm: token ids need the table and exclude a branch");
     TS_REQUIRE(width <= 48 * 1024, "stream_norm: rows of %d elements are not supported", width);
@@ -74,7 +91,7 @@ TS_API int ts_stream_norm(const void* branch, const float* w_close, float* strea
             cudaFuncSetAttribute(stream_norm_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         stream_norm_kernel<TYPE><<<count, threads, smem, stream_handle>>>(                                        \
             (const TYPE*)branch, w_close, stream, w_open, (TYPE*)out, rows, width, eps, (const TYPE*)table, ids,  \
-            table_rows, scale, write);                                                                            \
+            table_rows, scale, write, flags);                                                                          \
     } while (0)
     if (dtype == TS_F32) TS_STREAM_NORM(float);
     else if (dtype == TS_BF16) TS_STREAM_NORM(__nv_bfloat16);

@@ -78,7 +78,8 @@ class StepContext:
         table = self.tables[self._runner.manager.pool_of_group[base.group]] if base.group >= 0 else None
         return EntryBinding(base.k_pool, base.v_pool, base.page_stride, base.entry_offset, base.page_tokens,
                             base.num_pages, table, table.shape[1] if table is not None else 0,
-                            entry.writes_cache, base.group, base.state, self.state_slots)
+                            entry.writes_cache, base.group, base.state, self.state_slots, base.v_page_stride,
+                            base.v_entry_offset)
 
 
 GRAPH_MAX_TOKENS = 512      # the largest step with a prompt portion that is replayed from a graph (see StepRunner)

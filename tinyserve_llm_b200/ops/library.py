@@ -50,19 +50,27 @@ _SIGNATURES = {
     "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
     "ts_skinny_linear_gated": ("int", "pppiiilliffp"),
     "ts_gemm_tcgen05_gated": ("int", "pppiiilliffpp"),
-    "ts_stream_norm": ("int", "ppppppiifppifip"),
+    "ts_stream_norm": ("int", "ppppppiifppifiip"),
     "ts_linear_recurrence": ("int", "ppplllplppfffpipppiplpiiiipip"),
-    "ts_head_norm_gate": ("int", "pplppiiifip"),
+    "ts_head_norm_gate": ("int", "piplpippliiififip"),
     "ts_latent_prepare": ("int", "pliiippfppppplliipiiiip"),
     "ts_latent_attention": ("int", "pllpliipplliipipppiiiifiiplip"),
     "ts_latent_attention_scratch_floats": ("long long", "iiii"),
     "ts_set_latent_mma": ("void", "i"),
-    "ts_moe_route": ("int", "ppppppiiip"),
+    "ts_moe_route": ("int", "ppppppiiiip"),
     "ts_moe_arrange": ("int", "ppppppiip"),
-    "ts_moe_linear": ("int", "plpipipiipiiiffip"),
+    "ts_moe_linear": ("int", "plpipipiipiiiffpiip"),
     "ts_moe_combine": ("int", "pppppiiiip"),
     "ts_gated_activation": ("int", "ppiiiffip"),
     "ts_sgemm_nt_batched": ("int", "pppiiilllilllp"),
+    "ts_qk_norm_rope_store": ("int", "pliiipppppfpifpppppllllii" "piiiiiiiip"),
+    "ts_sigmoid_gate": ("int", "plplpliifip"),
+    "ts_paged_attention_split": ("int", "plpppllllii" "pippiiiiifiip"),
+    "ts_short_conv_silu": ("int", "plppppiplpiiiip"),
+    "ts_recurrence_scan": ("int", "ppliipppiplpiiiip"),
+    "ts_delta_prepare": ("int", "pplppppl" "ppiiiiffip"),
+    "ts_mlstm_prepare": ("int", "ppllpplppffppiplpppiiiip"),
+    "ts_row_scaled_activation": ("int", "ppppiiiip"),
 }
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 _RETURNS = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "void": None, "const char*": ctypes.c_char_p}
@@ -414,10 +422,12 @@ class Ops:
     # ------------------------------------------------------------------ float32 residual stream
     def stream_norm(self, branch: torch.Tensor | None, w_close: torch.Tensor | None, stream: torch.Tensor,
                     w_open: torch.Tensor | None, eps: float, dtype: torch.dtype, rows: torch.Tensor | None = None,
-                    table: torch.Tensor | None = None, ids: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor | None:
+                    table: torch.Tensor | None = None, ids: torch.Tensor | None = None, scale: float = 1.0,
+                    centered: bool = False, plain_add: bool = False) -> torch.Tensor | None:
         """
-        stream (float32, in place) += closing norm of `branch` (if given); returns the opening norm of
-        the sum in `dtype` (if `w_open` is given).  With `rows` only those rows are normed, into a
+        stream (float32, in place) += closing norm of `branch` (if given; with `plain_add` the branch as
+        it is); returns the opening norm of the sum in `dtype` (if `w_open` is given; with `centered` a
+        layer norm without bias instead of an RMS norm).  With `rows` only those rows are normed, into a
         compact output, and the stream is left as it is.  With `table` and `ids` the rows
         table[ids] * scale start the stream instead.  Weights are float32 and multiply as given.
         """
@@ -446,7 +456,7 @@ class Ops:
             out = torch.empty((count, width), dtype=dtype, device=stream.device)
         self._call("ts_stream_norm", _ptr(branch), _ptr(w_close), _ptr(stream), _ptr(w_open), _ptr(out), _ptr(rows), count,
                    width, eps, _ptr(table), _ptr(ids), table.shape[0] if table is not None else 0, scale,
-                   _DTYPE_CODE[dtype], _stream())
+                   (1 if centered else 0) | (2 if plain_add else 0), _DTYPE_CODE[dtype], _stream())
         return out
 
     # ------------------------------------------------------------------ linear recurrences
@@ -486,15 +496,204 @@ class Ops:
         return out
 
     def head_norm_gate(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, heads: int, vdim: int,
-                       eps: float, dtype: torch.dtype) -> torch.Tensor:
-        """[T, heads * vdim] in `dtype`: each head's o (float32) RMS-normed over vdim, times weight (if any), times silu(gate)."""
+                       eps: float, dtype: torch.dtype, *, gate_kind: str = "silu", weight_per_head: bool = False,
+                       log_max: torch.Tensor | None = None, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """
+        [T, heads * vdim] in `dtype`: each head's o (float32) RMS-normed over vdim, times weight (if any; one
+        stretch of vdim shared by the heads, or heads * vdim with `weight_per_head`), times silu or sigmoid of
+        the gate, times `scale`.  With `log_max` (float32 [T, heads]) o holds vdim + 1 columns a head and is
+        first divided by max(|o[.., vdim]|, exp(-log_max)) + 1e-6.  `out` may be a column stretch of a wider tensor.
+        """
         self._check(o, "o", torch.float32, 2)
-        if gate.stride(1) != 1 or gate.dtype != dtype or tuple(gate.shape) != tuple(o.shape):
+        T = o.shape[0]
+        o_head = vdim + 1 if log_max is not None else vdim
+        if o.shape[1] != heads * o_head:
+            raise KernelError(f"head_norm_gate: o has {o.shape[1]} columns, expected {heads * o_head}")
+        if gate.stride(1) != 1 or gate.dtype != dtype or tuple(gate.shape) != (T, heads * vdim):
             raise KernelError("head_norm_gate: the gate must be a [T, heads * vdim] slice of the activation dtype")
-        out = torch.empty(o.shape, dtype=dtype, device=o.device)
-        self._call("ts_head_norm_gate", _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), o.shape[0], heads, vdim,
-                   eps, _DTYPE_CODE[dtype], _stream())
+        if weight is not None and weight.numel() != (heads * vdim if weight_per_head else vdim):
+            raise KernelError(f"head_norm_gate: the weight has {weight.numel()} elements")
+        if gate_kind not in ("silu", "sigmoid"):
+            raise KernelError(f"head_norm_gate: gate kind {gate_kind!r}")
+        if out is None:
+            out = torch.empty((T, heads * vdim), dtype=dtype, device=o.device)
+        elif out.dtype != dtype or tuple(out.shape) != (T, heads * vdim) or out.stride(1) != 1:
+            raise KernelError("head_norm_gate: out must be a [T, heads * vdim] stretch of the activation dtype")
+        self._call("ts_head_norm_gate", _ptr(o), o_head, _ptr(gate), gate.stride(0), _ptr(weight),
+                   vdim if weight_per_head else 0, _ptr(log_max), _ptr(out), out.stride(0), T, heads, vdim, eps,
+                   1 if gate_kind == "sigmoid" else 0, scale, _DTYPE_CODE[dtype], _stream())
         return out
+
+    # ------------------------------------------------------------------ attention with normed queries and keys, gated recurrences
+    def qk_norm_rope_store(self, y: torch.Tensor, offsets: tuple[int, int, int], biases, weights, eps: float, position,
+                           ctx, binding, heads: int, kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+        """
+        From the projection's output y (q, k, v at the column `offsets`): biases added (float32 tensors or
+        None), q and k RMS-normed over the whole projection with `weights` (q's, k's; or None), rotated by
+        `position` (frequencies, dims, magnitude), k and v stored into the token's cache slot.  Returns q [T, heads * dim].
+        """
+        if y.dtype not in _DTYPE_CODE or y.dim() != 2 or y.stride(1) != 1:
+            raise KernelError("qk_norm_rope_store: y must be a [T, columns] stretch of an activation dtype")
+        if binding.k_pool.dtype != y.dtype:
+            raise KernelError(f"cache pool is {binding.k_pool.dtype} but activations are {y.dtype}")
+        T = y.shape[0]
+        q = torch.empty((T, heads * dim), dtype=y.dtype, device=y.device)
+        freq, rot, magnitude = None, 0, 1.0
+        if position is not None:
+            freq, rot, magnitude = position.frequencies, position.dims, float(getattr(position, "magnitude", 1.0))
+        qb, kb, vb = biases if biases is not None else (None, None, None)
+        qw, kw = weights if weights is not None else (None, None)
+        v_page_stride, v_entry_offset = binding.value_geometry()
+        self._call("ts_qk_norm_rope_store", _ptr(y), y.stride(0), offsets[0], offsets[1], offsets[2], _ptr(qb), _ptr(kb),
+                   _ptr(vb), _ptr(qw), _ptr(kw), eps, _ptr(freq), rot, magnitude, _ptr(ctx.positions),
+                   _ptr(ctx.seq_of_token), _ptr(q), _ptr(binding.k_pool), _ptr(binding.v_pool), binding.page_stride,
+                   binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens, binding.num_pages,
+                   _ptr(binding.block_table), binding.table_width, 1 if binding.writes else 0, T, heads, kv_heads, dim,
+                   vdim, _DTYPE_CODE[y.dtype], _stream())
+        return q
+
+    def paged_attention_split(self, q: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, vd: int, scale: float,
+                              window: int) -> torch.Tensor:
+        """
+        [T, nh * vd]: causal attention of q [T, nh * hd] over the entry's cached keys (head size hd) and
+        values (head size vd).  Equal head sizes of 64 or 128 in bfloat16 run on the tensor-core kernels
+        (`paged_attention`), everything else on the generic kernel.
+        """
+        self._check(q, "q", tuple(_DTYPE_CODE), 2)
+        if q.shape[1] != nh * hd:
+            raise KernelError(f"paged_attention_split: q has {q.shape[1]} columns, expected {nh * hd}")
+        if (hd == vd and q.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
+                and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
+            # the tensor-core kernels read q from the columns of a [q | k | v] row: q alone is such a row's first part
+            qkv = torch.empty((q.shape[0], (nh + 2 * nkv) * hd), dtype=q.dtype, device=q.device)
+            qkv[:, :nh * hd].copy_(q)
+            return self.paged_attention(qkv, ctx, binding, nh, nkv, hd, scale, window)
+        out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
+        v_page_stride, v_entry_offset = binding.value_geometry()
+        self._call("ts_paged_attention_split", _ptr(q), q.stride(0), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
+                   binding.page_stride, binding.entry_offset, v_page_stride, v_entry_offset, binding.page_tokens,
+                   binding.num_pages, _ptr(binding.block_table), binding.table_width, _ptr(ctx.positions),
+                   _ptr(ctx.seq_of_token), q.shape[0], nh, nkv, hd, vd, scale, window, _DTYPE_CODE[q.dtype], _stream())
+        return out
+
+    def sigmoid_gate(self, a: torch.Tensor, gate: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """a * sigmoid(gate) * scale, [T, cols]; the operands and `out` may be column stretches of wider tensors."""
+        if a.dtype not in _DTYPE_CODE or gate.dtype != a.dtype or a.shape != gate.shape or a.stride(1) != 1 or gate.stride(1) != 1:
+            raise KernelError("sigmoid_gate: a and gate must be [T, cols] stretches of one activation dtype")
+        if out is None:
+            out = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+        elif out.dtype != a.dtype or out.shape != a.shape or out.stride(1) != 1:
+            raise KernelError("sigmoid_gate: out must be a [T, cols] stretch of the activation dtype")
+        self._call("ts_sigmoid_gate", _ptr(a), a.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), a.shape[0],
+                   a.shape[1], scale, _DTYPE_CODE[a.dtype], _stream())
+        return out
+
+    @staticmethod
+    def _state_floats(binding, floats: int, what: str) -> tuple[torch.Tensor, int]:
+        if binding is None or binding.state is None or binding.state_slots is None:
+            raise KernelError(f"{what}: the cache entry has no state slot")
+        state = binding.state
+        if state.stride(1) != 1 or state.stride(0) % 4 or state.data_ptr() % 4 or state.shape[1] < floats * 4:
+            raise KernelError(f"{what}: the state rows are not float32-aligned or too small")
+        return state, state.stride(0) // 4
+
+    def short_conv_silu(self, x: torch.Tensor, taps: torch.Tensor, ctx, binding) -> torch.Tensor:
+        """
+        float32 [T, C]: silu of the causal convolution over time of x [T, C] (a column stretch) with
+        taps [C, K] (float32, the last column is the current token's); the K - 1 inputs before this step's
+        first token come from the request's state slot ([K - 1, C] float32), which is moved on.
+        """
+        if x.dtype not in _DTYPE_CODE or x.dim() != 2 or x.stride(1) != 1:
+            raise KernelError("short_conv_silu: x must be a [T, C] stretch of an activation dtype")
+        self._check(taps, "taps", torch.float32, 2)
+        T, C = x.shape
+        K = taps.shape[1]
+        if taps.shape[0] != C:
+            raise KernelError(f"short_conv_silu: {taps.shape[0]} filters for {C} channels")
+        state, stride = self._state_floats(binding, (K - 1) * C, "short_conv_silu")
+        y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        self._call("ts_short_conv_silu", _ptr(x), x.stride(0), _ptr(taps), _ptr(ctx.seq_of_token), _ptr(ctx.cu_q),
+                   _ptr(binding.state_slots), binding.state_slots.shape[0], state.data_ptr(), stride, _ptr(y), T, C, K,
+                   _DTYPE_CODE[x.dtype], _stream())
+        if K > 1:
+            self.launches += 1                               # the kernel that moves the slot on
+        return y
+
+    def recurrence_scan(self, prepared: torch.Tensor, v: torch.Tensor, ctx, binding, *, heads: int, dim: int, vdim: int,
+                        v_cols: int | None = None, beta: torch.Tensor | None = None) -> torch.Tensor:
+        """
+        float32 [T, heads * vdim]: the scan of `linear_recurrence` from inputs the caller prepared: prepared
+        float32 [3, T, heads * dim] (q, k, decay), v [T, heads * v_cols] (float32 or an activation dtype; value
+        columns from v_cols to vdim are the constant 1), `beta` float32 [T, heads] for the delta rule.
+        The state slot holds [heads, dim, vdim] floats.
+        """
+        T = prepared.shape[1]
+        v_cols = vdim if v_cols is None else v_cols
+        self._check(prepared, "prepared", torch.float32, 3)
+        if tuple(prepared.shape) != (3, T, heads * dim):
+            raise KernelError(f"recurrence_scan: prepared is {tuple(prepared.shape)}, expected {(3, T, heads * dim)}")
+        if v.dtype not in _DTYPE_CODE or v.dim() != 2 or v.stride(1) != 1 or tuple(v.shape) != (T, heads * v_cols):
+            raise KernelError(f"recurrence_scan: v must be a [T, {heads * v_cols}] stretch")
+        if beta is not None:
+            self._check(beta, "beta", torch.float32, 2)
+            if tuple(beta.shape) != (T, heads):
+                raise KernelError(f"recurrence_scan: beta is {tuple(beta.shape)}, expected {(T, heads)}")
+        state, stride = self._state_floats(binding, heads * dim * vdim, "recurrence_scan")
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=v.device)
+        self._call("ts_recurrence_scan", _ptr(prepared), _ptr(v), v.stride(0), v_cols, _DTYPE_CODE[v.dtype], _ptr(beta),
+                   _ptr(ctx.cu_q), _ptr(binding.state_slots), binding.state_slots.shape[0], state.data_ptr(), stride,
+                   _ptr(out), heads, dim, vdim, T, _stream())
+        return out
+
+    def delta_prepare(self, q: torch.Tensor, k: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                      b: torch.Tensor, *, heads: int, kv_heads: int, dim: int, unit_eps: float, q_scale: float):
+        """
+        (prepared [3, T, heads * dim], beta [T, heads]), float32, for the delta rule's scan: q, k (float32
+        [T, kv_heads * dim] stretches with one row stride) as unit vectors per head, q scaled; decays
+        exp(-exp(a_log) softplus(z + dt_bias)); beta = sigmoid(b).
+        """
+        T = q.shape[0]
+        for t, name, cols in ((q, "q", kv_heads * dim), (k, "k", kv_heads * dim)):
+            if t.dtype != torch.float32 or t.stride(1) != 1 or tuple(t.shape) != (T, cols):
+                raise KernelError(f"delta_prepare: {name} must be a float32 [T, {cols}] stretch")
+        if q.stride(0) != k.stride(0):
+            raise KernelError("delta_prepare: q and k must share a row stride")
+        self._check(z, "decay logits", torch.float32, 2)
+        if tuple(z.shape) != (T, heads * dim) or b.dtype not in _DTYPE_CODE or b.stride(1) != 1 or tuple(b.shape) != (T, heads):
+            raise KernelError("delta_prepare: decay logits [T, heads * dim] and beta logits [T, heads] are needed")
+        prepared = torch.empty((3, T, heads * dim), dtype=torch.float32, device=q.device)
+        beta = torch.empty((T, heads), dtype=torch.float32, device=q.device)
+        self._call("ts_delta_prepare", _ptr(q), _ptr(k), q.stride(0), _ptr(z), _ptr(dt_bias), _ptr(a_log), _ptr(b),
+                   b.stride(0), _ptr(prepared), _ptr(beta), T, heads, kv_heads, dim, unit_eps, q_scale,
+                   _DTYPE_CODE[b.dtype], _stream())
+        return prepared, beta
+
+    def mlstm_prepare(self, q: torch.Tensor, k: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor,
+                      ctx, binding, *, heads: int, dim: int, cap: float, q_scale: float, max_offset_floats: int):
+        """
+        (prepared [3, T, heads * dim], log_max [T, heads]) for the scan of a matrix memory with exponential
+        gates.  q, k: [T, heads * dim] stretches of one activation dtype; gates: float32 [T, 2 heads],
+        input gates then forget gates, before bias and cap.  The running maxima ([heads] floats) live
+        `max_offset_floats` floats into the request's state slot.
+        """
+        T = q.shape[0]
+        for t, name in ((q, "q"), (k, "k")):
+            if t.dtype not in _DTYPE_CODE or t.stride(1) != 1 or tuple(t.shape) != (T, heads * dim) or t.dtype != q.dtype:
+                raise KernelError(f"mlstm_prepare: {name} must be a [T, {heads * dim}] stretch of the activation dtype")
+        if gates.dtype != torch.float32 or gates.stride(1) != 1 or tuple(gates.shape) != (T, 2 * heads):
+            raise KernelError("mlstm_prepare: the gates must be float32 [T, 2 heads]")
+        state, stride = self._state_floats(binding, max_offset_floats + heads, "mlstm_prepare")
+        dev = q.device
+        prepared = torch.empty((3, T, heads * dim), dtype=torch.float32, device=dev)
+        log_max = torch.empty((T, heads), dtype=torch.float32, device=dev)
+        factors = torch.empty((2, T, heads), dtype=torch.float32, device=dev)
+        self._call("ts_mlstm_prepare", _ptr(q), _ptr(k), q.stride(0), k.stride(0), _ptr(gates),
+                   gates.data_ptr() + heads * gates.element_size(), gates.stride(0), _ptr(bias_i), _ptr(bias_f), cap, q_scale,
+                   _ptr(ctx.cu_q), _ptr(binding.state_slots), binding.state_slots.shape[0],
+                   state.data_ptr() + 4 * max_offset_floats, stride, _ptr(log_max), _ptr(factors), _ptr(prepared), T, heads,
+                   dim, _DTYPE_CODE[q.dtype], _stream())
+        self.launches += 1                                   # gates, then what enters the scan
+        return prepared, log_max
 
     # ------------------------------------------------------------------ attention over a cached latent
     def latent_prepare(self, y: torch.Tensor, ctx, binding, q_rank: int, rank: int, rot: int, q_weight: torch.Tensor,
@@ -595,11 +794,14 @@ class Ops:
                    limit, alpha, _DTYPE_CODE[gate_up.dtype], _stream())
         return out
 
-    def moe_route(self, logits: torch.Tensor, bias: torch.Tensor | None, ctx, top: int):
+    def moe_route(self, logits: torch.Tensor, bias: torch.Tensor | None, ctx, top: int, scoring: str = "softmax_chosen"):
         """
         Routing of one step: (chosen [T, top] int32, share [T, top] float32, offsets [E + 1] int32 of the
         experts' stretches, pair_of_row [T * top], row_of_pair [T * top]).  All on the device; nothing is read back.
+        `scoring`: "softmax_chosen" (shares = softmax over the chosen logits) or "sigmoid" (sigmoid of each chosen logit).
         """
+        if scoring not in ("softmax_chosen", "sigmoid"):
+            raise KernelError(f"moe_route: scoring {scoring!r}")
         self._check(logits, "router logits", torch.float32, 2)
         T, E = logits.shape
         dev = logits.device
@@ -611,18 +813,25 @@ class Ops:
         row_of_pair = torch.empty((T * top,), dtype=torch.int32, device=dev)
         seq_of_token = getattr(ctx, "seq_of_token", None)
         self._call("ts_moe_route", _ptr(logits), _ptr(bias), _ptr(seq_of_token), _ptr(chosen), _ptr(share), _ptr(counters),
-                   T, E, top, _stream())
+                   T, E, top, 1 if scoring == "sigmoid" else 0, _stream())
         self._call("ts_moe_arrange", _ptr(chosen), _ptr(counters), counters.data_ptr() + 4 * E, _ptr(offsets),
                    _ptr(pair_of_row), _ptr(row_of_pair), T * top, E, _stream())
         return chosen, share, offsets, pair_of_row, row_of_pair
 
     def moe_linear(self, x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, pair_of_row: torch.Tensor | None, top: int,
-                   pairs: int, activation: str | None = None, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
+                   pairs: int, activation: str | None = None, limit: float = 0.0, alpha: float = 1.0,
+                   row_scale: torch.Tensor | None = None) -> torch.Tensor:
         """
         [pairs, N] (or [pairs, N / 2] with a gated `activation`): sorted row r of expert e times w[e]^T,
         w [E, N, K].  With `pair_of_row` the input row of sorted row r is x[pair_of_row[r] // top]
-        (tokens gathered); without, x[r] (the rows are sorted already).
+        (tokens gathered); without, x[r] (the rows are sorted already).  `activation` "relu2" is ungated:
+        relu(s)^2 of the product s, which `row_scale` (float32, one factor a pair) multiplies first.
         """
+        unary = 1 if activation == "relu2" else 0
+        if unary:
+            activation = None
+        if row_scale is not None:
+            self._check(row_scale, "row scale", torch.float32)
         self._check(x, "x", tuple(_DTYPE_CODE), 2)
         self._check(w, "expert weights", x.dtype, 3)
         E, N, K = w.shape
@@ -636,22 +845,26 @@ class Ops:
             self.calls["library_grouped_mm"] = self.calls.get("library_grouped_mm", 0) + 1
             rows = x if pair_of_row is None else x.index_select(0, torch.div(pair_of_row, top, rounding_mode="floor"))
             full = torch._grouped_mm(rows, w.transpose(1, 2), offs=offsets[1:])
+            if unary or row_scale is not None:
+                self._call("ts_row_scaled_activation", _ptr(full), _ptr(pair_of_row), _ptr(row_scale), _ptr(full), pairs, N,
+                           unary, _DTYPE_CODE[x.dtype], _stream())
+                return full
             return self.gated_activation(full, activation, limit, alpha) if gated else full
         out = torch.empty((pairs, N // 2 if gated else N), dtype=x.dtype, device=x.device)
         self._call("ts_moe_linear", _ptr(x), x.stride(0), _ptr(pair_of_row), top, _ptr(offsets), E, _ptr(w), N, K, _ptr(out),
                    pairs, 1 if gated else 0, self.GATED_ACTIVATIONS[activation] if gated else 0, limit, alpha,
-                   _DTYPE_CODE[x.dtype], _stream())
+                   _ptr(row_scale), unary, _DTYPE_CODE[x.dtype], _stream())
         return out
 
-    def moe_combine(self, y: torch.Tensor, row_of_pair: torch.Tensor, share: torch.Tensor, shared_out: torch.Tensor | None,
-                    num_tokens: int) -> torch.Tensor:
-        """[T, width]: sum over a token's choices of share * y[row of the pair], plus the shared expert's output."""
+    def moe_combine(self, y: torch.Tensor, row_of_pair: torch.Tensor, share: torch.Tensor | None,
+                    shared_out: torch.Tensor | None, num_tokens: int) -> torch.Tensor:
+        """[T, width]: sum over a token's choices of share * y[row of the pair] (share None: 1), plus the shared expert's output."""
         self._check(y, "y", tuple(_DTYPE_CODE), 2)
         if shared_out is not None:
             self._check(shared_out, "shared expert output", y.dtype, 2)
         out = torch.empty((num_tokens, y.shape[1]), dtype=y.dtype, device=y.device)
         self._call("ts_moe_combine", _ptr(y), _ptr(row_of_pair), _ptr(share), _ptr(shared_out), _ptr(out), num_tokens,
-                   y.shape[1], share.shape[1], _DTYPE_CODE[y.dtype], _stream())
+                   y.shape[1], row_of_pair.shape[0] // max(num_tokens, 1), _DTYPE_CODE[y.dtype], _stream())
         return out
 
     def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:

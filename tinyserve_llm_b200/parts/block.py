@@ -3,7 +3,8 @@ Arrangements: how a block wires its mixer, feed-forward and norms.
 
 "pre_norm" is the reference's decoder layer (model/llama.py:238-253): the residual add is deferred
 into the following norm, so a block takes and returns (branch output, residual stream).
-"sandwich_norm" also norms each sublayer's output and keeps the stream in float32.
+"sandwich_norm" also norms each sublayer's output and keeps the stream in float32;
+"pre_norm_stream" is the pre-norm wiring around a float32 stream.
 """
 
 from __future__ import annotations
@@ -118,3 +119,43 @@ class SandwichNormBlock:
             return branch, residual
         h, residual = self.feed_forward_norm.forward(branch, residual)
         return PendingBranch(self.feed_forward.forward(h, ctx), self.feed_forward_post_norm), residual
+
+
+@register_arrangement("pre_norm_stream")
+class PreNormStreamBlock(PreNormBlock):
+    """
+    x = x + mixer(norm1(x)); x = x + ffn(norm2(x)) around a residual stream kept in float32: a sublayer's
+    output travels on as a `PendingBranch` without a closing norm, and the next norm of the stream (the
+    next block's first, or the model's final one) adds it and norms the sum in one kernel.  A block
+    without a feed-forward ends after its mixer.
+    """
+
+    takes_token_ids = True
+
+    @staticmethod
+    def _members(spec: BlockSpec):
+        members = [("norm", spec.mixer_norm, spec.mixer_norm_prefix), ("mixer", spec.mixer, spec.mixer_prefix)]
+        if spec.feed_forward is not None:
+            members += [("norm", spec.feed_forward_norm, spec.feed_forward_norm_prefix),
+                        ("feed_forward", spec.feed_forward, spec.feed_forward_prefix)]
+        return members
+
+    def __init__(self, spec: BlockSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.spec = spec
+        built = [part_class(role, part)(part, _sub(tensors, prefix), rt) for role, part, prefix in self._members(spec)]
+        self.mixer_norm, self.mixer = built[:2]
+        self.feed_forward_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm, self.feed_forward = built[2:]
+
+    def forward(self, x, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None):
+        from tinyserve_llm_b200.parts.norm import PendingBranch
+        if embedding is not None:
+            h, residual = self.mixer_norm.forward_embedded(embedding, x)
+        else:
+            h, residual = self.mixer_norm.forward(x, residual)
+        branch = PendingBranch(self.mixer.forward(h, ctx, binding), None)
+        if self.feed_forward is None:
+            return branch, residual
+        h, residual = self.feed_forward_norm.forward(branch, residual)
+        return PendingBranch(self.feed_forward.forward(h, ctx), None), residual

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from tinyserve_llm_b200.config.spec import GatedMLPSpec
+from tinyserve_llm_b200.config.spec import GatedMLPSpec, PlainMLPSpec
 from tinyserve_llm_b200.parts.base import FeedForward, Runtime, TensorDecl, register_part
 from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
@@ -43,3 +43,30 @@ class GatedMLP(FeedForward):
         spec, ops = self.spec, self.rt.ops
         # the gate/up products carry the activation in their epilogue where there is a kernel of the engine's own for the size
         return self.down(ops.linear_gated(x, self.gate_up.weight, spec.activation, spec.limit, spec.alpha))
+
+
+@register_part("feed_forward", "plain_mlp")
+class PlainMLP(FeedForward):
+    """Ungated feed-forward down(act(up(x))) with act the square of relu."""
+
+    graph_safe = True
+
+    ACTIVATIONS = ("relu2",)
+
+    @classmethod
+    def declare(cls, spec: PlainMLPSpec) -> dict[str, TensorDecl]:
+        up, down = spec.tensor_names
+        return {up: TensorDecl((spec.intermediate_size, spec.hidden_size)),
+                down: TensorDecl((spec.hidden_size, spec.intermediate_size))}
+
+    def __init__(self, spec: PlainMLPSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        super().__init__(spec, tensors, rt)
+        if spec.activation not in self.ACTIVATIONS:
+            raise NotImplementedError(f"activation {spec.activation!r} is not supported; have {self.ACTIVATIONS}")
+        up, down = spec.tensor_names
+        self.up = Linear(tensors[up], rt)
+        self.down = Linear(tensors[down], rt)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        h = self.up(x)
+        return self.down(torch.relu(h).square_())

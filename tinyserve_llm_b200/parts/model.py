@@ -12,8 +12,8 @@ from __future__ import annotations
 import torch
 
 from tinyserve_llm_b200.config.spec import ModelSpec
-from tinyserve_llm_b200.parts import (attention, latent_attention, mlp, norm, recurrence, rotary,  # noqa: F401  (registration)
-                                      routed_experts)
+from tinyserve_llm_b200.parts import (attention, delta_rule, gated_attention, latent_attention, mlp, mlstm,  # noqa: F401  (registration)
+                                      norm, parallel, recurrence, rotary, routed_experts)
 from tinyserve_llm_b200.parts.base import KVNeed, Runtime, TensorDecl, arrangement_class, part_class
 from tinyserve_llm_b200.parts.block import _sub
 from tinyserve_llm_b200.parts.linear import Linear

@@ -50,7 +50,7 @@ class PendingBranch:
 
     __slots__ = ("tensor", "closing")
 
-    def __init__(self, tensor: torch.Tensor, closing: "StreamRMSNorm") -> None:
+    def __init__(self, tensor: torch.Tensor, closing: "StreamRMSNorm | None") -> None:
         self.tensor = tensor
         self.closing = closing
 
@@ -65,6 +65,7 @@ class StreamRMSNorm(Norm):
     """
 
     graph_safe = True
+    centered = False          # a subclass norms around the mean (layer norm)
 
     @classmethod
     def declare(cls, spec) -> dict[str, TensorDecl]:
@@ -79,10 +80,13 @@ class StreamRMSNorm(Norm):
     def forward(self, x, residual: torch.Tensor | None, rows: torch.Tensor | None = None):
         if residual is None:
             raise ValueError("a stream norm needs the residual stream (the first norm starts it from the embedding)")
-        branch, closing = (x.tensor, x.closing.weight) if isinstance(x, PendingBranch) else (None, None)
-        if x is not None and branch is None:
+        branch = closing = None
+        if isinstance(x, PendingBranch):
+            branch, closing = x.tensor, (x.closing.weight if x.closing is not None else None)
+        elif x is not None:
             raise ValueError("a stream norm takes a PendingBranch (a sublayer's output and its closing norm) or nothing")
-        out = self.rt.ops.stream_norm(branch, closing, residual, self.weight, self.eps, self.rt.dtype, rows=rows)
+        out = self.rt.ops.stream_norm(branch, closing, residual, self.weight, self.eps, self.rt.dtype, rows=rows,
+                                      centered=self.centered, plain_add=branch is not None and closing is None)
         return out, residual
 
     def close(self, branch: torch.Tensor, residual: torch.Tensor) -> None:
@@ -92,5 +96,15 @@ class StreamRMSNorm(Norm):
     def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0):
         residual = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
         out = self.rt.ops.stream_norm(None, None, residual, self.weight, self.eps, self.rt.dtype, table=table, ids=ids,
-                                      scale=scale)
+                                      scale=scale, centered=self.centered)
         return out, residual
+
+
+@register_part("norm", "layernorm_stream")
+class StreamLayerNorm(StreamRMSNorm):
+    """
+    Layer norm with a weight and no bias beside a float32 residual stream:
+    y = (s - mean(s)) / sqrt(mean((s - mean(s))^2) + eps) * w, statistics, weight and stream in float32.
+    """
+
+    centered = True

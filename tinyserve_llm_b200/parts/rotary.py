@@ -52,6 +52,22 @@ class Rotary(PositionEncoding):
         self.table = rt.shared[key]
 
 
+def yarn_frequencies(dims: int, base: float, yarn) -> torch.Tensor:
+    """float64 [dims / 2]: base^(-2i/dims), rescaled by `yarn` (a `YarnScaling`) where given."""
+    i = torch.arange(0, dims // 2, dtype=torch.float64)
+    freq = float(base) ** (-2.0 * i / dims)
+    if yarn is None:
+        return freq
+
+    def turns(t: float) -> float:
+        return dims * math.log(yarn.original / (2 * math.pi * t)) / (2 * math.log(base))
+
+    lo = max(math.floor(turns(yarn.fast)), 0)
+    hi = min(math.ceil(turns(yarn.slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return freq / yarn.factor * ramp + freq * (1.0 - ramp)
+
+
 @register_part("position", "rotary_inline")
 class InlineRotary(PositionEncoding):
     """
@@ -66,7 +82,8 @@ class InlineRotary(PositionEncoding):
             raise ValueError(f"rotation over {spec.dims} channels: the number must be positive and even")
         key = ("rotary_inline", spec)
         if key not in rt.shared:
-            exponent = torch.arange(0, spec.dims, 2, dtype=torch.float64) / spec.dims
-            rt.shared[key] = (1.0 / (float(spec.base) ** exponent)).to(torch.float32).to(rt.device)
+            rt.shared[key] = yarn_frequencies(spec.dims, float(spec.base), spec.yarn).to(torch.float32).to(rt.device)
         self.dims = spec.dims
         self.frequencies = rt.shared[key]
+        # cos and sin are multiplied by this (1 without YaRN); a kernel that rotates with a YaRN rescaling has to apply it
+        self.magnitude = 1.0 if spec.yarn is None else 0.1 * math.log(spec.yarn.factor) + 1.0

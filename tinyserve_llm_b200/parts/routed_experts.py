@@ -10,13 +10,18 @@ One step runs: the router product, routing and a sort of the (token, choice) pai
 device (nothing is read back, so the step can be replayed from a CUDA graph), one grouped product
 gate/up with the activation in its epilogue, one grouped product down, and the weighted sum.  The
 experts' weights are stacked [experts, 2 ff, width] and [experts, width, ff].
+
+Variants, by the spec: `scoring` "sigmoid" weighs a chosen expert by sigmoid(z) without renormalising;
+`weight_on` "input" multiplies the expert's input by the weight instead of its output (experts without
+a gate, `PlainMLPSpec`: down(relu(up(w h))^2) = down(relu(w * up(h))^2), so the weight goes into the
+first product's epilogue and the outputs are summed unweighted).
 """
 
 from __future__ import annotations
 
 import torch
 
-from tinyserve_llm_b200.config.spec import RoutedExpertsSpec
+from tinyserve_llm_b200.config.spec import GatedMLPSpec, RoutedExpertsSpec
 from tinyserve_llm_b200.parts.base import FeedForward, Runtime, TensorDecl, part_class, register_part
 from tinyserve_llm_b200.parts.linear import Linear
 
@@ -30,6 +35,10 @@ class RoutedExperts(FeedForward):
         if spec.expert is None or not 0 < spec.top <= spec.num_experts:
             raise ValueError(f"routed experts need an expert description and 0 < top <= experts, got top={spec.top}, "
                              f"experts={spec.num_experts}")
+        if spec.scoring not in ("softmax_chosen", "sigmoid") or spec.weight_on not in ("output", "input"):
+            raise NotImplementedError(f"routed experts: scoring {spec.scoring!r}, weight on {spec.weight_on!r}")
+        if isinstance(spec.expert, GatedMLPSpec) and spec.weight_on == "input":
+            raise NotImplementedError("routed experts: a weight on the input is built for experts without a gate")
         expert_class = part_class("feed_forward", spec.expert)
         out = {spec.router_name: TensorDecl((spec.num_experts, spec.hidden_size))}
         if spec.router_bias_name:
@@ -45,10 +54,16 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec: RoutedExpertsSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
         self.declare(spec)
-        gate, up, down = spec.expert.tensor_names
         pre = [spec.expert_prefix.format(e) for e in range(spec.num_experts)]
         to = dict(device=rt.device, dtype=rt.dtype)
-        self.gate_up = torch.stack([torch.cat([tensors[p + gate], tensors[p + up]], dim=0) for p in pre]).to(**to).contiguous()
+        self.gated = isinstance(spec.expert, GatedMLPSpec)
+        if self.gated:
+            gate, up, down = spec.expert.tensor_names
+            self.gate_up = torch.stack([torch.cat([tensors[p + gate], tensors[p + up]], dim=0) for p in pre]).to(**to).contiguous()
+        else:
+            up, down = spec.expert.tensor_names
+            part_class("feed_forward", spec.expert)          # the expert's kind is known
+            self.gate_up = torch.stack([tensors[p + up] for p in pre]).to(**to).contiguous()
         self.down = torch.stack([tensors[p + down] for p in pre]).to(**to).contiguous()
         self.router = Linear(tensors[spec.router_name], rt)
         self.router_bias = None
@@ -63,9 +78,14 @@ class RoutedExperts(FeedForward):
         spec, ops = self.spec, self.rt.ops
         T, top = x.shape[0], spec.top
         logits = self.router(x, out_dtype=torch.float32)
-        _, share, offsets, pair_of_row, row_of_pair = ops.moe_route(logits, self.router_bias, ctx, top)
+        _, share, offsets, pair_of_row, row_of_pair = ops.moe_route(logits, self.router_bias, ctx, top, spec.scoring)
         e = spec.expert
-        hidden = ops.moe_linear(x, self.gate_up, offsets, pair_of_row, top, T * top, e.activation, e.limit, e.alpha)
+        on_input = spec.weight_on == "input"
+        if self.gated:
+            hidden = ops.moe_linear(x, self.gate_up, offsets, pair_of_row, top, T * top, e.activation, e.limit, e.alpha)
+        else:
+            hidden = ops.moe_linear(x, self.gate_up, offsets, pair_of_row, top, T * top, e.activation,
+                                    row_scale=share if on_input else None)
         y = ops.moe_linear(hidden, self.down, offsets, None, top, T * top)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
-        return ops.moe_combine(y, row_of_pair, share, shared, T)
+        return ops.moe_combine(y, row_of_pair, None if on_input else share, shared, T)
