@@ -1,15 +1,15 @@
 """
-Prefill and decode throughput of the Duduvik decoder at layer sizes that resemble a real model's,
-beside the Llama decoder at equal width and depth, both with random weights through the engine's
-own step function:
+Prefill and decode throughput of a design at layer sizes that resemble a real model's, beside the
+engine's closest other design at equal width and depth (Duduvik beside Llama, Nipizen beside
+Duduvik), both with random weights through the engine's own step function:
 
-    python bench.py --design duduvik [--size small|medium|large] [--steps K] [--warmup W]
+    python bench.py --design duduvik|nipizen [--size small|medium|large] [--steps K] [--warmup W]
 
 For each design: a prompt of `prefill` tokens in one step (launched kernel by kernel), and decode
 steps of `batch` requests at `context` tokens each (replayed from a CUDA graph), timed on the device
 with CUDA events after warm-up; between timed steps a buffer larger than L2 is written.  One JSON
-line per design goes to standard output, then one line with the kernels of a Duduvik prefill step
-and of a decode step by their share of the device time (torch.profiler, a run of its own, not timed).
+line per design goes to standard output, then one line with the kernels of the named design's prefill
+step and of a decode step by their share of the device time (torch.profiler, a run of its own, not timed).
 """
 
 from __future__ import annotations
@@ -46,6 +46,28 @@ def duduvik_config(s: dict) -> dict:
     layers = [dict(mixers[i % 3], mlp=ffs[i % 2]) for i in range(s["layers"])]
     return {"architecture": "Duduvik", "vocab": VOCAB, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
             "layers": layers}
+
+
+def nipizen_config(s: dict) -> dict:
+    """
+    Layers in the order parallel (attention beside a gated delta rule) / matrix memory / parallel, every one
+    with routed experts (top 4).  Attention heads of 128 channels for keys and values, so that the
+    tensor-core attention kernels take them; recurrent heads of 128 key channels.
+    """
+    width, heads = s["width"], s["heads"]
+    dim = width // heads                                   # 128 at every size
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                              "rot": {"base": 10000.0, "dims": dim // 2,
+                                      "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+                     "right": {"heads": heads // 2, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "conv": 4,
+                               "decay_rank": 16, "gate_rank": 16},
+                     "left_scale": 0.7, "right_scale": 0.7}}
+    mem = {"type": "mlstm", "mixer": {"heads": heads // 2, "dim": dim, "vdim": 2 * dim, "gate_cap": 15.0}}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": 4}, "expert": {"ff": s["expert_ff"]}}
+    mixers = (par, mem, par)
+    return {"architecture": "Nipizen", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6},
+            "layers": [dict(mixers[i % 3], mlp=moe) for i in range(s["layers"])]}
 
 
 def llama_config(s: dict) -> dict:
@@ -172,10 +194,14 @@ def _tensors(model):
 
 
 def run(design: str, size: str, steps: int, warmup: int, peaks: dict) -> int:
-    if design != "duduvik":
-        raise SystemExit(f"--design {design!r}: have ['duduvik']")
     s = SIZES[size]
-    for name, cfg, profile in (("llama", llama_config(s), False), ("duduvik", duduvik_config(s), True)):
+    if design == "duduvik":
+        pair = (("llama", llama_config(s), False), ("duduvik", duduvik_config(s), True))
+    elif design == "nipizen":
+        pair = (("duduvik", duduvik_config(s), True), ("nipizen", nipizen_config(s), True))
+    else:
+        raise SystemExit(f"--design {design!r}: have ['duduvik', 'nipizen']")
+    for name, cfg, profile in pair:
         record = {"design": name, "size": size, "width": s["width"], "layers": s["layers"], "dtype": "bf16",
                   "data": "synthetic", "timing": "CUDA events, median, L2 flushed between timed steps", "peaks": peaks}
         record.update(measure(cfg, s, steps, warmup, profile))
