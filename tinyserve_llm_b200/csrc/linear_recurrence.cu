@@ -107,10 +107,16 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     const int jj = DELTA ? threadIdx.x / LR_ROWGROUPS : threadIdx.x % LR_COLS, j = j0 + jj;
     const bool live = j < vdim;
     float* st = p.state + (long long)slot * p.slot_stride + (long long)h * dim * vdim;
+    // Which rows of its column a thread holds.  Plain: a run of MAXM rows.  Delta rule: four rows out of every 64, so that
+    // the sixteen lanes of a column read one contiguous stretch of a staged row with each 16-byte load (a run a lane
+    // would put the lanes' loads 4 * MAXM bytes apart: two to four passes through shared memory a load)
+    auto row_of = [&](int m) { return DELTA ? (m >> 2) * (4 * LR_ROWGROUPS) + 4 * r + (m & 3) : r * MAXM + m; };
+    const int first = DELTA ? 4 * r : r * MAXM;           // floats from a staged row's start to this thread's first 16 bytes
+    constexpr int STEP4 = DELTA ? LR_ROWGROUPS : 1;       // float4s between a thread's consecutive 16-byte loads
     float S[MAXM];
 #pragma unroll
     for (int m = 0; m < MAXM; ++m) {
-        const int i = r * MAXM + m;
+        const int i = row_of(m);
         S[m] = (live && i < dim) ? st[(long long)i * vdim + j] : 0.f;
     }
     const T* v = (const T*)p.v;
@@ -154,55 +160,95 @@ linear_recurrence_kernel(RecurrenceArgs p) {
         if (DELTA && threadIdx.x < LR_TILE) b_s[threadIdx.x] = raw_b;
         if (t0 + LR_TILE < end) fetch(t0 + LR_TILE, min(LR_TILE, end - t0 - LR_TILE));   // under way during this tile's work
         __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            const float vj = v_s[tt * LR_COLS + jj];
-            const float4* qt = reinterpret_cast<const float4*>(q_s + tt * PITCH + r * MAXM);
-            const float4* kt = reinterpret_cast<const float4*>(k_s + tt * PITCH + r * MAXM);
-            const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + r * MAXM);
-            float acc = 0.f;
-            if (DELTA) {
-                float kreg[MAXM];
-                float read = 0.f;
+        if (DELTA) {
+            // The chain from one token's state to the next's is decay, S^T k, four shuffles, the correction.  What a
+            // token needs from shared memory is loaded one token ahead, so that the chain waits for nothing else; its
+            // sums are kept in four pieces so that no piece waits for more than MAXM / 4 products.
+            float4 kc[MAXM / 4], ac4[MAXM / 4], qc[MAXM / 4];
+            float vc, bc;
+            auto load_token = [&](int tt, float4 (&k4)[MAXM / 4], float4 (&a4)[MAXM / 4], float4 (&q4)[MAXM / 4], float& vv,
+                                  float& bb) {
+                const float4* qt = reinterpret_cast<const float4*>(q_s + tt * PITCH + first);
+                const float4* kt = reinterpret_cast<const float4*>(k_s + tt * PITCH + first);
+                const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + first);
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) { k4[m4] = kt[m4 * STEP4]; a4[m4] = at[m4 * STEP4]; q4[m4] = qt[m4 * STEP4]; }
+                vv = v_s[tt * LR_COLS + jj];
+                bb = b_s[tt];
+            };
+            load_token(0, kc, ac4, qc, vc, bc);
+            for (int tt = 0; tt < n; ++tt) {
+                float4 kn[MAXM / 4], an[MAXM / 4], qn[MAXM / 4];
+                float vn, bn;
+                load_token(min(tt + 1, LR_TILE - 1), kn, an, qn, vn, bn);      // the tile's last row again: not used
+                float rd[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) {
-                    const float4 k4 = kt[m4], a4 = at[m4];
-                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+                    const float kk[4] = {kc[m4].x, kc[m4].y, kc[m4].z, kc[m4].w};
+                    const float aa[4] = {ac4[m4].x, ac4[m4].y, ac4[m4].z, ac4[m4].w};
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int m = 4 * m4 + c;
-                        kreg[m] = kk[c];
                         S[m] *= aa[c];
-                        read = fmaf(S[m], kk[c], read);
+                        rd[c] = fmaf(S[m], kk[c], rd[c]);
                     }
                 }
+                float read = (rd[0] + rd[1]) + (rd[2] + rd[3]);
 #pragma unroll
                 for (int o = LR_ROWGROUPS / 2; o > 0; o >>= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-                const float u = b_s[tt] * (vj - read);
+                const float u = bc * (vc - read);
+                float ac[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) {
-                    const float4 q4 = qt[m4];
-                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+                    const float kk[4] = {kc[m4].x, kc[m4].y, kc[m4].z, kc[m4].w};
+                    const float qq[4] = {qc[m4].x, qc[m4].y, qc[m4].z, qc[m4].w};
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int m = 4 * m4 + c;
-                        S[m] = fmaf(kreg[m], u, S[m]);
-                        acc = fmaf(S[m], qq[c], acc);
+                        S[m] = fmaf(kk[c], u, S[m]);
+                        ac[c] = fmaf(S[m], qq[c], ac[c]);
                     }
                 }
-            } else {
+                part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = (ac[0] + ac[1]) + (ac[2] + ac[3]);
 #pragma unroll
-                for (int m4 = 0; m4 < MAXM / 4; ++m4) {
-                    const float4 q4 = qt[m4], k4 = kt[m4], a4 = at[m4];
-                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int m = 4 * m4 + c;
-                        S[m] = fmaf(aa[c], S[m], kk[c] * vj);
-                        acc = fmaf(S[m], qq[c], acc);
-                    }
-                }
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) { kc[m4] = kn[m4]; ac4[m4] = an[m4]; qc[m4] = qn[m4]; }
+                vc = vn;
+                bc = bn;
             }
-            part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
+        } else {
+            // no thread waits for another here; a token's staged inputs are loaded one token ahead of their use
+            float4 kc[MAXM / 4], ac4[MAXM / 4], qc[MAXM / 4];
+            float vc;
+            auto load_token = [&](int tt, float4 (&k4)[MAXM / 4], float4 (&a4)[MAXM / 4], float4 (&q4)[MAXM / 4], float& vv) {
+                const float4* qt = reinterpret_cast<const float4*>(q_s + tt * PITCH + first);
+                const float4* kt = reinterpret_cast<const float4*>(k_s + tt * PITCH + first);
+                const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + first);
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) { k4[m4] = kt[m4]; a4[m4] = at[m4]; q4[m4] = qt[m4]; }
+                vv = v_s[tt * LR_COLS + jj];
+            };
+            load_token(0, kc, ac4, qc, vc);
+            for (int tt = 0; tt < n; ++tt) {
+                float4 kn[MAXM / 4], an[MAXM / 4], qn[MAXM / 4];
+                float vn;
+                load_token(min(tt + 1, LR_TILE - 1), kn, an, qn, vn);          // the tile's last row again: not used
+                float acc = 0.f;
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) {
+                    const float qq[4] = {qc[m4].x, qc[m4].y, qc[m4].z, qc[m4].w}, kk[4] = {kc[m4].x, kc[m4].y, kc[m4].z, kc[m4].w};
+                    const float aa[4] = {ac4[m4].x, ac4[m4].y, ac4[m4].z, ac4[m4].w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = 4 * m4 + c;
+                        S[m] = fmaf(aa[c], S[m], kk[c] * vc);
+                        acc = fmaf(S[m], qq[c], acc);
+                    }
+                }
+                part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
+#pragma unroll
+                for (int m4 = 0; m4 < MAXM / 4; ++m4) { kc[m4] = kn[m4]; ac4[m4] = an[m4]; qc[m4] = qn[m4]; }
+                vc = vn;
+            }
         }
         __syncthreads();
         for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
@@ -216,7 +262,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     }
 #pragma unroll
     for (int m = 0; m < MAXM; ++m) {
-        const int i = r * MAXM + m;
+        const int i = row_of(m);
         if (live && i < dim) st[(long long)i * vdim + j] = S[m];
     }
 }

@@ -62,30 +62,35 @@ __global__ void qk_norm_rope_store_kernel(QKPrepareArgs p) {
         const float x = to_float<T>(y[e]) + (bias ? bias[e] : 0.f);
         return weight ? x * inv * weight[e] : x;
     };
-    auto rotated = [&](const T* y, const float* bias, const float* weight, float inv, int e) {
-        const int i = e % p.dim;
-        const float x = element(y, bias, weight, inv, e);
-        if (!p.freq || i >= p.rot) return x;
-        const int f = i < half ? i : i - half;
-        const float other = element(y, bias, weight, inv, i < half ? e + half : e - half);
-        float sn, cs;
-        sincosf((float)pos * p.freq[f], &sn, &cs);
-        sn *= p.magnitude;
-        cs *= p.magnitude;
-        return i < half ? x * cs - other * sn : x * cs + other * sn;      // (u cos - v sin, v cos + u sin)
+    // One thread a rotated pair (i, i + rot/2): one sincosf for both; channels past `rot` pass unchanged.
+    auto rotate_into = [&](const T* y, const float* bias, const float* weight, float inv, int n, auto&& store) {
+        for (int e = threadIdx.x; e < n; e += blockDim.x) {
+            const int i = e % p.dim;
+            if (p.freq && i < p.rot) {
+                if (i >= half) continue;                   // written by the pair's first channel
+                const float u = element(y, bias, weight, inv, e), v = element(y, bias, weight, inv, e + half);
+                float sn, cs;
+                sincosf((float)pos * p.freq[i], &sn, &cs);
+                sn *= p.magnitude;
+                cs *= p.magnitude;
+                store(e, u * cs - v * sn);
+                store(e + half, v * cs + u * sn);
+            } else {
+                store(e, element(y, bias, weight, inv, e));
+            }
+        }
     };
-    for (int e = threadIdx.x; e < nq; e += blockDim.x)
-        q_out[e] = from_float<T>(rotated(yq, p.q_bias, p.q_weight, inv_q, e));
+    rotate_into(yq, p.q_bias, p.q_weight, inv_q, nq, [&](int e, float x) { q_out[e] = from_float<T>(x); });
     if (!p.writes) return;
     const int page = p.block_table[(long long)seq * p.table_width + pos / p.k_geo.page_tokens];
     if (page < 0 || page >= p.k_geo.num_pages) return;
     const int slot = pos % p.k_geo.page_tokens;
     T* kp = (T*)p.k_pool + (long long)page * p.k_geo.page_stride + p.k_geo.entry_offset;
     T* vp = (T*)p.v_pool + (long long)page * p.v_geo.page_stride + p.v_geo.entry_offset;
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+    rotate_into(yk, p.k_bias, p.k_weight, inv_k, nk, [&](int e, float x) {
         const int h = e / p.dim, i = e % p.dim;
-        kp[((long long)h * p.k_geo.page_tokens + slot) * p.dim + i] = from_float<T>(rotated(yk, p.k_bias, p.k_weight, inv_k, e));
-    }
+        kp[((long long)h * p.k_geo.page_tokens + slot) * p.dim + i] = from_float<T>(x);
+    });
     for (int e = threadIdx.x; e < nv; e += blockDim.x) {
         const int h = e / p.vdim, i = e % p.vdim;
         vp[((long long)h * p.v_geo.page_tokens + slot) * p.vdim + i] =
@@ -110,7 +115,8 @@ TS_API int ts_qk_norm_rope_store(const void* y, long long y_stride, int q_off, i
                     KVGeometry{k_page_stride, k_entry_offset, page_tokens, num_pages},
                     KVGeometry{v_page_stride, v_entry_offset, page_tokens, num_pages}, block_table, table_width, writes,
                     heads, kv_heads, dim, vdim};
-    const int threads = heads * dim >= 2048 ? 512 : 256;
+    // many tokens: small CTAs, many of them on an SM (a CTA's life is a chain of loads and two sums); few tokens: wide ones
+    const int threads = num_tokens >= 512 ? 128 : (heads * dim >= 2048 ? 512 : 256);
     if (dtype == TS_F32) qk_norm_rope_store_kernel<float><<<num_tokens, threads, 0, stream>>>(p);
     else if (dtype == TS_BF16) qk_norm_rope_store_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(p);
     else return ts_fail("qk_norm_rope_store: unknown dtype code %d", dtype);

@@ -65,7 +65,7 @@ TS_API int ts_delta_prepare(const float* q, const float* k, long long qk_stride,
 }
 
 // One warp a (request, head): 32 tokens at a time, each lane its token's gates; the running maximum is carried
-// through the lanes in order.  factors[0] = decay, factors[1] = the key's factor, each [tokens, heads].
+// through the lanes by a scan.  factors[0] = decay, factors[1] = the key's factor, each [tokens, heads].
 __global__ void mlstm_gates_kernel(const float* __restrict__ gi, const float* __restrict__ gf, long long gate_stride,
                                    const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
                                    const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
@@ -87,14 +87,18 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ gi, const float* __
             i_gate = cap * tanhf((gi[(long long)t * gate_stride + h] + bias_i[h]) / cap);
             f_gate = log_sigmoid_f(cap * tanhf((gf[(long long)t * gate_stride + h] + bias_f[h]) / cap));
         }
-        float before = 0.f, after = 0.f;
-        const int n = min(32, end - t0);
-        for (int s = 0; s < n; ++s) {
-            const float fs = __shfl_sync(0xffffffffu, f_gate, s), is = __shfl_sync(0xffffffffu, i_gate, s);
-            const float next = fmaxf(fs + m, is);
-            if (lane == s) { before = m; after = next; }
-            m = next;
+        // m_t = max(f_t + m_(t-1), i_t) is the composition of the maps x -> max(x + a, b); an inclusive scan over the
+        // lanes composes them: (a, b) after (a', b') = (a' + a, max(b' + a, b)).  Lanes past the end hold the identity.
+        float a = t < end ? f_gate : 0.f, b = t < end ? i_gate : -INFINITY;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float pa = __shfl_up_sync(0xffffffffu, a, o), pb = __shfl_up_sync(0xffffffffu, b, o);
+            if (lane >= o) { b = fmaxf(pb + a, b); a = pa + a; }
         }
+        const float after = fmaxf(m + a, b);
+        float before = __shfl_up_sync(0xffffffffu, after, 1);
+        if (lane == 0) before = m;
+        m = __shfl_sync(0xffffffffu, after, 31);          // lanes past the end carry the last token's value on
         if (t < end) {
             const long long at = (long long)t * heads + h;
             log_max[at] = after;
