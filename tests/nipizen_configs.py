@@ -60,4 +60,9 @@ WIDE = model(512, 128, 1e-6, [
     (parallel(attention(2, 1, 32, 96, 0.18, 8), delta(2, 2, 64, 64, 4, 8, 8), 0.5, 2.0), moe(3, 3, 32)),
 ])
 
+# heads of 128 channels, three query heads a key/value head (the tensor-core attention's other head size)
+GROUPED = model(257, 128, 1e-5, [
+    (parallel(attention(6, 2, 128, 128, 0.09, 64, scaling=(2.0, 256, 16.0, 4.0)), delta(2, 2, 32, 32, 4, 8, 8), 0.9, 1.1), moe(4, 2, 32)),
+])
+
 WEIGHTS = {"std": 0.08, "unit_std": 0.25}

@@ -24,9 +24,9 @@ import plain_nipizen as plain
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CONFIGS = {"mixed": C.MIXED, "recurrent": C.RECURRENT, "wide": C.WIDE}
-SEEDS = {"mixed": 111, "recurrent": 222, "wide": 333}
-PAGE = {"mixed": 16, "recurrent": 16, "wide": 64}
+CONFIGS = {"mixed": C.MIXED, "recurrent": C.RECURRENT, "wide": C.WIDE, "grouped": C.GROUPED}
+SEEDS = {"mixed": 111, "recurrent": 222, "wide": 333, "grouped": 444}
+PAGE = {"mixed": 16, "recurrent": 16, "wide": 64, "grouped": 64}
 
 
 def read_tensors(folder):

@@ -10,7 +10,7 @@
 // projections on is float32: rotation, decays, the state, the sums.
 //
 // One kernel serves prompts, portions of prompts and single decoded tokens: a CTA owns one request,
-// one head and 16 value channels, reads the state from the request's slot, walks over the request's
+// one head and 16 value channels (8 for the delta rule), reads the state from the request's slot, walks over the request's
 // tokens of this step in order and writes the state back.  The arithmetic of a token does not depend
 // on where the step was cut or on what else is in the batch.  A first kernel computes what enters
 // the recurrence (rotated and scaled q and k, the decays) once per token, head and channel; the scan
@@ -33,9 +33,8 @@
 #include "common.cuh"
 
 constexpr int LR_ROWGROUPS = 16;    // thread (r, j) holds rows r * MAXM .. r * MAXM + MAXM - 1 of column j of the state
-constexpr int LR_COLS = 16;         // value channels of a CTA
 constexpr int LR_TILE = 16;         // tokens staged at a time
-static_assert(LR_TILE * LR_COLS == LR_ROWGROUPS * LR_COLS, "a thread stages one value of v a tile");
+static_assert(LR_TILE == LR_ROWGROUPS, "a thread stages one value of v a tile: tokens x columns = row groups x columns");
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -83,8 +82,10 @@ struct RecurrenceArgs {
     int heads, dim, vdim;
 };
 
-template <typename T, int MAXM, bool DELTA>
-__global__ void __launch_bounds__(LR_ROWGROUPS * LR_COLS)
+// COLS: value channels of a CTA (16; the delta rule, whose tokens are a chain of dependent steps, runs 8 a CTA so that
+// a prompt alone spreads over twice the SMs)
+template <typename T, int MAXM, bool DELTA, int COLS>
+__global__ void __launch_bounds__(LR_ROWGROUPS * COLS)
 linear_recurrence_kernel(RecurrenceArgs p) {
     // staged rows are padded with zeros to LR_ROWGROUPS * MAXM channels: the inner loop needs no bound and reads
     // four channels a load
@@ -94,17 +95,17 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     float* q_s = smem;                                   // [LR_TILE][PITCH]
     float* k_s = q_s + LR_TILE * PITCH;
     float* a_s = k_s + LR_TILE * PITCH;
-    float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][LR_COLS]
-    float* part = v_s + LR_TILE * LR_COLS;               // [LR_TILE][LR_ROWGROUPS][LR_COLS]
-    float* b_s = part + LR_TILE * LR_ROWGROUPS * LR_COLS; // [LR_TILE] (delta rule)
-    const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * LR_COLS;
+    float* v_s = a_s + LR_TILE * PITCH;                  // [LR_TILE][COLS]
+    float* part = v_s + LR_TILE * COLS;               // [LR_TILE][LR_ROWGROUPS][COLS]
+    float* b_s = part + LR_TILE * LR_ROWGROUPS * COLS; // [LR_TILE] (delta rule)
+    const int seq = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * COLS;
     const int slot = p.slots[seq];
     const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
     if (slot < 0 || end <= begin) return;                // a padding request, or one that feeds nothing
     // plain: the threads of a row group are neighbours (their loads of a state row coalesce); delta rule: the
     // sixteen row groups of a column are the lanes of half a warp
-    const int r = DELTA ? threadIdx.x % LR_ROWGROUPS : threadIdx.x / LR_COLS;
-    const int jj = DELTA ? threadIdx.x / LR_ROWGROUPS : threadIdx.x % LR_COLS, j = j0 + jj;
+    const int r = DELTA ? threadIdx.x % LR_ROWGROUPS : threadIdx.x / COLS;
+    const int jj = DELTA ? threadIdx.x / LR_ROWGROUPS : threadIdx.x % COLS, j = j0 + jj;
     const bool live = j < vdim;
     float* st = p.state + (long long)slot * p.slot_stride + (long long)h * dim * vdim;
     // Which rows of its column a thread holds.  Plain: a run of MAXM rows.  Delta rule: four rows out of every 64, so that
@@ -123,14 +124,14 @@ linear_recurrence_kernel(RecurrenceArgs p) {
     const long long row_width = (long long)p.heads * dim;
     // What a tile needs from global memory is asked for one tile ahead and held in registers while the tile
     // before it is worked on.
-    constexpr int ROUNDS = LR_TILE * PITCH / (LR_ROWGROUPS * LR_COLS);
+    constexpr int ROUNDS = LR_TILE * PITCH / (LR_ROWGROUPS * COLS);
     float raw_q[ROUNDS], raw_k[ROUNDS], raw_a[ROUNDS];
     T raw_v;                                             // as loaded: converting would wait for the load
     float raw_b = 0.f;
     auto fetch = [&](int t0, int n) {
 #pragma unroll
         for (int round = 0; round < ROUNDS; ++round) {
-            const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
+            const int e = round * (LR_ROWGROUPS * COLS) + threadIdx.x;
             const int tt = e / PITCH, i = e % PITCH;
             raw_q[round] = raw_k[round] = raw_a[round] = 0.f;
             if (tt < n && i < dim) {
@@ -140,7 +141,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
                 raw_a[round] = p.prepared[2 * p.total + at];
             }
         }
-        const int tt = threadIdx.x / LR_COLS, c = threadIdx.x % LR_COLS;       // LR_TILE * LR_COLS = one value a thread
+        const int tt = threadIdx.x / COLS, c = threadIdx.x % COLS;       // LR_TILE * COLS = one value a thread
         raw_v = from_float<T>(j0 + c >= p.v_cols && j0 + c < vdim ? 1.f : 0.f);
         if (tt < n && j0 + c < p.v_cols) raw_v = v[(long long)(t0 + tt) * p.v_stride + (long long)h * p.v_cols + j0 + c];
         if (DELTA && threadIdx.x < LR_TILE) raw_b = threadIdx.x < n ? p.beta[(long long)(t0 + threadIdx.x) * p.heads + h] : 0.f;
@@ -151,7 +152,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
         __syncthreads();                                 // the tile before has been read
 #pragma unroll
         for (int round = 0; round < ROUNDS; ++round) {
-            const int e = round * (LR_ROWGROUPS * LR_COLS) + threadIdx.x;
+            const int e = round * (LR_ROWGROUPS * COLS) + threadIdx.x;
             q_s[e] = raw_q[round];
             k_s[e] = raw_k[round];
             a_s[e] = raw_a[round];
@@ -173,7 +174,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
                 const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + first);
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) { k4[m4] = kt[m4 * STEP4]; a4[m4] = at[m4 * STEP4]; q4[m4] = qt[m4 * STEP4]; }
-                vv = v_s[tt * LR_COLS + jj];
+                vv = v_s[tt * COLS + jj];
                 bb = b_s[tt];
             };
             load_token(0, kc, ac4, qc, vc, bc);
@@ -209,7 +210,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
                         ac[c] = fmaf(S[m], qq[c], ac[c]);
                     }
                 }
-                part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = (ac[0] + ac[1]) + (ac[2] + ac[3]);
+                part[(tt * LR_ROWGROUPS + r) * COLS + jj] = (ac[0] + ac[1]) + (ac[2] + ac[3]);
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) { kc[m4] = kn[m4]; ac4[m4] = an[m4]; qc[m4] = qn[m4]; }
                 vc = vn;
@@ -225,7 +226,7 @@ linear_recurrence_kernel(RecurrenceArgs p) {
                 const float4* at = reinterpret_cast<const float4*>(a_s + tt * PITCH + first);
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) { k4[m4] = kt[m4]; a4[m4] = at[m4]; q4[m4] = qt[m4]; }
-                vv = v_s[tt * LR_COLS + jj];
+                vv = v_s[tt * COLS + jj];
             };
             load_token(0, kc, ac4, qc, vc);
             for (int tt = 0; tt < n; ++tt) {
@@ -244,19 +245,19 @@ linear_recurrence_kernel(RecurrenceArgs p) {
                         acc = fmaf(S[m], qq[c], acc);
                     }
                 }
-                part[(tt * LR_ROWGROUPS + r) * LR_COLS + jj] = acc;
+                part[(tt * LR_ROWGROUPS + r) * COLS + jj] = acc;
 #pragma unroll
                 for (int m4 = 0; m4 < MAXM / 4; ++m4) { kc[m4] = kn[m4]; ac4[m4] = an[m4]; qc[m4] = qn[m4]; }
                 vc = vn;
             }
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < n * LR_COLS; e += blockDim.x) {
-            const int tt = e / LR_COLS, c = e % LR_COLS;
+        for (int e = threadIdx.x; e < n * COLS; e += blockDim.x) {
+            const int tt = e / COLS, c = e % COLS;
             if (j0 + c >= vdim) continue;
             float o = 0.f;
 #pragma unroll
-            for (int g = 0; g < LR_ROWGROUPS; ++g) o += part[(tt * LR_ROWGROUPS + g) * LR_COLS + c];
+            for (int g = 0; g < LR_ROWGROUPS; ++g) o += part[(tt * LR_ROWGROUPS + g) * COLS + c];
             p.out[(long long)(t0 + tt) * p.heads * vdim + (long long)h * vdim + j0 + c] = o;
         }
     }
@@ -269,24 +270,24 @@ linear_recurrence_kernel(RecurrenceArgs p) {
 
 template <typename T>
 static int launch_recurrence(const RecurrenceArgs& p, int num_seqs, cudaStream_t stream) {
-    dim3 grid((p.vdim + LR_COLS - 1) / LR_COLS, p.heads, num_seqs);
-#define TS_RECURRENCE(MAXM, DELTA)                                                                                 \
+#define TS_RECURRENCE(MAXM, DELTA, COLS)                                                                           \
     do {                                                                                                           \
-        const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * LR_COLS +                       \
-                                     LR_TILE * LR_ROWGROUPS * LR_COLS + LR_TILE) * sizeof(float);                  \
+        const dim3 grid((p.vdim + COLS - 1) / COLS, p.heads, num_seqs);                                            \
+        const size_t smem = (size_t)(3 * LR_TILE * LR_ROWGROUPS * MAXM + LR_TILE * COLS +                          \
+                                     LR_TILE * LR_ROWGROUPS * COLS + LR_TILE) * sizeof(float);                     \
         if (smem > 48 * 1024)                                                                                      \
-            cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)smem);                                                                       \
-        linear_recurrence_kernel<T, MAXM, DELTA><<<grid, LR_ROWGROUPS * LR_COLS, smem, stream>>>(p);               \
+            cudaFuncSetAttribute(linear_recurrence_kernel<T, MAXM, DELTA, COLS>,                                   \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
+        linear_recurrence_kernel<T, MAXM, DELTA, COLS><<<grid, LR_ROWGROUPS * COLS, smem, stream>>>(p);            \
     } while (0)
     if (p.beta) {
-        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, true);
-        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, true);
-        else TS_RECURRENCE(16, true);
+        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, true, 8);
+        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, true, 8);
+        else TS_RECURRENCE(16, true, 16);
     } else {
-        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, false);
-        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, false);
-        else TS_RECURRENCE(16, false);
+        if (p.dim <= 4 * LR_ROWGROUPS) TS_RECURRENCE(4, false, 16);
+        else if (p.dim <= 8 * LR_ROWGROUPS) TS_RECURRENCE(8, false, 16);
+        else TS_RECURRENCE(16, false, 16);
     }
 #undef TS_RECURRENCE
     TS_LAUNCH_CHECK("linear_recurrence");
