@@ -412,17 +412,31 @@ TS_API int ts_gated_activation(const void* gate_up, void* out, int num_tokens, i
 }
 
 // out[r, c] = act(x[r, c] * scale[pair of sorted row r]) for the ungated activations (after a library product).
-template <typename T>
+// VEC: 16 bytes a thread (the row width is a multiple of that many elements and the pointers are aligned).
+template <typename T, bool VEC>
 __global__ void row_scaled_activation_kernel(const T* __restrict__ x, const int* __restrict__ pair_of_row,
                                              const float* __restrict__ row_scale, T* __restrict__ out, long long total,
                                              int cols, int unary) {
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (long long)gridDim.x * blockDim.x) {
+    constexpr int VN = VEC ? 16 / (int)sizeof(T) : 1;
+    for (long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VN; idx < total;
+         idx += (long long)gridDim.x * blockDim.x * VN) {
         const long long r = idx / cols;
-        float v = to_float<T>(x[idx]);
-        if (row_scale) v *= row_scale[pair_of_row ? pair_of_row[r] : r];
-        if (unary == 1) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
-        out[idx] = from_float<T>(v);
+        const float c = row_scale ? row_scale[pair_of_row ? pair_of_row[r] : r] : 1.f;
+        if (VEC) {
+            uint4 raw = *reinterpret_cast<const uint4*>(x + idx);
+            T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                float f = to_float<T>(v[i]) * c;
+                if (unary == 1) f = fmaxf(f, 0.f) * fmaxf(f, 0.f);
+                v[i] = from_float<T>(f);
+            }
+            *reinterpret_cast<uint4*>(out + idx) = raw;
+        } else {
+            float f = to_float<T>(x[idx]) * c;
+            if (unary == 1) f = fmaxf(f, 0.f) * fmaxf(f, 0.f);
+            out[idx] = from_float<T>(f);
+        }
     }
 }
 
@@ -431,15 +445,21 @@ TS_API int ts_row_scaled_activation(const void* x, const int* pair_of_row, const
     TS_REQUIRE(rows >= 0 && cols > 0, "row_scaled_activation: bad sizes");
     if (rows == 0) return 0;
     const long long total = (long long)rows * cols;
-    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == TS_F32)
-        row_scaled_activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, pair_of_row, row_scale, (float*)out,
-                                                                        total, cols, unary);
-    else if (dtype == TS_BF16)
-        row_scaled_activation_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, pair_of_row, row_scale,
-                                                                                (__nv_bfloat16*)out, total, cols, unary);
-    else
-        return ts_fail("row_scaled_activation: unknown dtype code %d", dtype);
+    const int elem = dtype == TS_F32 ? 4 : 2, vn = 16 / elem;
+    const bool vec = cols % vn == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const long long threads = vec ? total / vn : total;
+    const unsigned blocks = (unsigned)((threads + 255) / 256 < 148 * 16 ? (threads + 255) / 256 : 148 * 16);
+#define TS_ROW_SCALED(TYPE)                                                                                         \
+    do {                                                                                                            \
+        if (vec) row_scaled_activation_kernel<TYPE, true><<<blocks, 256, 0, stream>>>(                              \
+            (const TYPE*)x, pair_of_row, row_scale, (TYPE*)out, total, cols, unary);                                \
+        else row_scaled_activation_kernel<TYPE, false><<<blocks, 256, 0, stream>>>(                                 \
+            (const TYPE*)x, pair_of_row, row_scale, (TYPE*)out, total, cols, unary);                                \
+    } while (0)
+    if (dtype == TS_F32) TS_ROW_SCALED(float);
+    else if (dtype == TS_BF16) TS_ROW_SCALED(__nv_bfloat16);
+    else return ts_fail("row_scaled_activation: unknown dtype code %d", dtype);
+#undef TS_ROW_SCALED
     TS_LAUNCH_CHECK("row_scaled_activation");
     return 0;
 }

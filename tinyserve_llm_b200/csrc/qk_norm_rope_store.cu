@@ -38,26 +38,29 @@ __global__ void qk_norm_rope_store_kernel(QKPrepareArgs p) {
     const T* yq = row + p.q_off;
     const T* yk = row + p.k_off;
     const T* yv = row + p.v_off;
-    float inv_q = 1.f, inv_k = 1.f;
-    if (p.q_weight) {
-        float acc = 0.f;
-        for (int e = threadIdx.x; e < nq; e += blockDim.x) {
-            const float x = to_float<T>(yq[e]) + (p.q_bias ? p.q_bias[e] : 0.f);
-            acc += x * x;
-        }
-        inv_q = 1.f / sqrtf(block_sum(acc, scratch) / (float)nq + p.eps);
-        __syncthreads();
-    }
-    if (p.k_weight) {
-        float acc = 0.f;
-        for (int e = threadIdx.x; e < nk; e += blockDim.x) {
-            const float x = to_float<T>(yk[e]) + (p.k_bias ? p.k_bias[e] : 0.f);
-            acc += x * x;
-        }
-        inv_k = 1.f / sqrtf(block_sum(acc, scratch) / (float)nk + p.eps);
-    }
+    // what does not depend on the sums is asked for first: the position and the page
     const int pos = p.positions[t];
     const int half = p.rot / 2;
+    const int page = p.writes ? p.block_table[(long long)seq * p.table_width + pos / p.k_geo.page_tokens] : -1;
+    float inv_q = 1.f, inv_k = 1.f;
+    if (p.q_weight || p.k_weight) {                   // both sums in one pass over the row, then two reductions
+        float acc_q = 0.f, acc_k = 0.f;
+        if (p.q_weight)
+            for (int e = threadIdx.x; e < nq; e += blockDim.x) {
+                const float x = to_float<T>(yq[e]) + (p.q_bias ? p.q_bias[e] : 0.f);
+                acc_q += x * x;
+            }
+        if (p.k_weight)
+            for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+                const float x = to_float<T>(yk[e]) + (p.k_bias ? p.k_bias[e] : 0.f);
+                acc_k += x * x;
+            }
+        if (p.q_weight) {
+            inv_q = 1.f / sqrtf(block_sum(acc_q, scratch) / (float)nq + p.eps);
+            __syncthreads();
+        }
+        if (p.k_weight) inv_k = 1.f / sqrtf(block_sum(acc_k, scratch) / (float)nk + p.eps);
+    }
     auto element = [&](const T* y, const float* bias, const float* weight, float inv, int e) {
         const float x = to_float<T>(y[e]) + (bias ? bias[e] : 0.f);
         return weight ? x * inv * weight[e] : x;
@@ -81,9 +84,7 @@ __global__ void qk_norm_rope_store_kernel(QKPrepareArgs p) {
         }
     };
     rotate_into(yq, p.q_bias, p.q_weight, inv_q, nq, [&](int e, float x) { q_out[e] = from_float<T>(x); });
-    if (!p.writes) return;
-    const int page = p.block_table[(long long)seq * p.table_width + pos / p.k_geo.page_tokens];
-    if (page < 0 || page >= p.k_geo.num_pages) return;
+    if (!p.writes || page < 0 || page >= p.k_geo.num_pages) return;
     const int slot = pos % p.k_geo.page_tokens;
     T* kp = (T*)p.k_pool + (long long)page * p.k_geo.page_stride + p.k_geo.entry_offset;
     T* vp = (T*)p.v_pool + (long long)page * p.v_geo.page_stride + p.v_geo.entry_offset;
