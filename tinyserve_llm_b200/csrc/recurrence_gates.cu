@@ -80,12 +80,21 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ gi, const float* __
     if (slot < 0 || end <= begin) return;
     float* m_state = state + (long long)slot * slot_stride + h;
     float m = *m_state;
+    const float bi = bias_i[h], bf = bias_f[h];
+    // a round's projections are loaded one round ahead of their use
+    float next_i = begin + lane < end ? gi[(long long)(begin + lane) * gate_stride + h] : 0.f;
+    float next_f = begin + lane < end ? gf[(long long)(begin + lane) * gate_stride + h] : 0.f;
     for (int t0 = begin; t0 < end; t0 += 32) {
         const int t = t0 + lane;
+        const float raw_i = next_i, raw_f = next_f;
+        if (t + 32 < end) {
+            next_i = gi[(long long)(t + 32) * gate_stride + h];
+            next_f = gf[(long long)(t + 32) * gate_stride + h];
+        }
         float i_gate = 0.f, f_gate = 0.f;
         if (t < end) {
-            i_gate = cap * tanhf((gi[(long long)t * gate_stride + h] + bias_i[h]) / cap);
-            f_gate = log_sigmoid_f(cap * tanhf((gf[(long long)t * gate_stride + h] + bias_f[h]) / cap));
+            i_gate = cap * tanhf((raw_i + bi) / cap);
+            f_gate = log_sigmoid_f(cap * tanhf((raw_f + bf) / cap));
         }
         // m_t = max(f_t + m_(t-1), i_t) is the composition of the maps x -> max(x + a, b); an inclusive scan over the
         // lanes composes them: (a, b) after (a', b') = (a' + a, max(b' + a, b)).  Lanes past the end hold the identity.

@@ -8,28 +8,34 @@
 // the first, moves the slot on.  Sums are float32; the output is float32.
 #include "common.cuh"
 
-// grid: (channel blocks, tokens); a CTA's threads are neighbouring channels of one token
+// grid: (channel blocks, groups of `group` tokens); a CTA's threads are neighbouring channels, each walks the group's
+// tokens (8 in a step of many tokens, 1 in a small step, where the walk would only lengthen the step)
+
 template <typename T>
 __global__ void short_conv_silu_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
                                        const int* __restrict__ seq_of_token, const int* __restrict__ cu_q,
                                        const int* __restrict__ slots, const float* __restrict__ state, long long slot_stride,
-                                       float* __restrict__ y, int channels, int taps) {
-    const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+                                       float* __restrict__ y, int num_tokens, int channels, int taps, int group) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
-    const int seq = seq_of_token[t];
-    if (seq < 0) { y[(long long)t * channels + c] = 0.f; return; }      // a padding row
-    const int slot = slots[seq];
-    const int begin = cu_q[seq];
-    const float* st = state + (long long)slot * slot_stride;
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-        const int src = t - begin - (taps - 1 - j);        // token of this step, or (negative) one of the slot's
-        float v;
-        if (src >= 0) v = to_float<T>(x[(long long)(begin + src) * x_stride + c]);
-        else v = slot >= 0 ? st[(long long)(taps - 1 + src) * channels + c] : 0.f;
-        acc = fmaf(w[(long long)c * taps + j], v, acc);
+    const int t_end = min(num_tokens, (int)(blockIdx.y + 1) * group);
+    const float* wc = w + (long long)c * taps;
+    for (int t = blockIdx.y * group; t < t_end; ++t) {
+        const int seq = seq_of_token[t];
+        if (seq < 0) { y[(long long)t * channels + c] = 0.f; continue; }      // a padding row
+        const int slot = slots[seq];
+        const int begin = cu_q[seq];
+        const float* st = state + (long long)slot * slot_stride;
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = t - begin - (taps - 1 - j);    // token of this step, or (negative) one of the slot's
+            float v;
+            if (src >= 0) v = to_float<T>(x[(long long)(begin + src) * x_stride + c]);
+            else v = slot >= 0 ? st[(long long)(taps - 1 + src) * channels + c] : 0.f;
+            acc = fmaf(wc[j], v, acc);
+        }
+        y[(long long)t * channels + c] = acc / (1.f + expf(-acc));
     }
-    y[(long long)t * channels + c] = acc / (1.f + expf(-acc));
 }
 
 // state <- the last taps - 1 inputs after this step; one thread a (request, channel), oldest entry first, so an
@@ -58,18 +64,19 @@ TS_API int ts_short_conv_silu(const void* x, long long x_stride, const float* w,
     TS_REQUIRE(num_tokens >= 0 && channels > 0 && taps > 0, "short_conv: bad sizes");
     TS_REQUIRE(slot_stride >= (long long)(taps - 1) * channels, "short_conv: a state slot is too small");
     if (num_tokens == 0 || num_seqs == 0) return 0;
-    TS_REQUIRE(num_tokens <= 65535, "short_conv: %d tokens a step are not supported (up to 65535)", num_tokens);
-    const dim3 blocks((channels + 255) / 256, num_tokens);
+    const int group = num_tokens >= 512 ? 8 : 1;
+    TS_REQUIRE(num_tokens <= 65535 * group, "short_conv: %d tokens a step are not supported", num_tokens);
+    const dim3 blocks((channels + 255) / 256, (num_tokens + group - 1) / group);
     const unsigned blocks2 = (unsigned)(((long long)num_seqs * channels + 255) / 256);
     if (dtype == TS_F32) {
         short_conv_silu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, x_stride, w, seq_of_token, cu_q, slots,
-                                                                  state, slot_stride, y, channels, taps);
+                                                                  state, slot_stride, y, num_tokens, channels, taps, group);
         if (taps > 1)
             short_conv_advance_kernel<float><<<blocks2, 256, 0, stream>>>((const float*)x, x_stride, cu_q, slots, state,
                                                                           slot_stride, num_seqs, channels, taps);
     } else if (dtype == TS_BF16) {
         short_conv_silu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, w, seq_of_token,
-                                                                          cu_q, slots, state, slot_stride, y, channels, taps);
+                                                                          cu_q, slots, state, slot_stride, y, num_tokens, channels, taps, group);
         if (taps > 1)
             short_conv_advance_kernel<__nv_bfloat16><<<blocks2, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, cu_q, slots,
                                                                                   state, slot_stride, num_seqs, channels, taps);
