@@ -37,13 +37,29 @@ def read_tensors(folder):
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
+    """
+    Per configuration a model folder for the float32 comparisons (the sharp ones, routing included) and one
+    for the bfloat16 comparisons in which every token uses all experts of a layer (same tensors, `top` =
+    `experts`): with fewer, a token whose router scores at the edge of the chosen set lie closer than
+    bfloat16's rounding of its activations takes another expert than the float64 model, and what it then
+    writes into the states and the cache reaches the tokens after it; a fifth of the positions of these small
+    models would be compared with the wrong thing.  Routing in bfloat16 is compared by the test of the routed
+    feed-forward alone.
+    """
+    import copy
     from tinyserve_llm_b200.weights import write_random_model
     out = {}
     for name, raw in CONFIGS.items():
         folder = str(tmp_path_factory.mktemp(f"nipizen_{name}"))
         write_random_model(folder, raw, SEEDS[name], **C.WEIGHTS)
         out[name, "float32"] = folder
-        out[name, "bfloat16"] = folder
+        every = copy.deepcopy(raw)
+        for layer in every["layers"]:
+            if layer["mlp"] is not None:
+                layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+        steady = str(tmp_path_factory.mktemp(f"nipizen_{name}_every_expert"))
+        write_random_model(steady, every, SEEDS[name], **C.WEIGHTS)
+        out[name, "bfloat16"] = steady
     return out
 
 
@@ -58,7 +74,10 @@ _PLAIN = {}
 def plain_logits(name, folder, ids):
     key = (folder, tuple(ids))
     if key not in _PLAIN:
-        _PLAIN[key] = plain.forward(CONFIGS[name], read_tensors(folder), ids)
+        with open(os.path.join(folder, "config.json")) as f:
+            raw = json.load(f)
+        assert raw["vocab"] == CONFIGS[name]["vocab"]
+        _PLAIN[key] = plain.forward(raw, read_tensors(folder), ids)
     return _PLAIN[key]
 
 
@@ -107,17 +126,17 @@ class Engine:
 def close(got, want, dtype):
     """
     float32: every position to rounding (the sharp comparison, of every mechanism and every schedule).
-    bfloat16: the error's root mean square against the logits' own spread, in the median and in the bulk.
-    Single positions may be far off: a token whose router scores at the edge of the chosen set lie closer
-    than bfloat16's rounding of its activations takes another expert than the float64 model, and what
-    it then writes into the states and the cache reaches the tokens after it (the models here are small).
+    bfloat16 (models in which every expert is used, see `folders`): the error's root mean square against the
+    logits' own spread, in the bulk and in the median; one position in a hundred (at least one) may be far off: a
+    matrix memory that holds one token reads out sign(k . q) v after its norm, so a first token whose k . q is
+    near zero hangs on bfloat16's rounding of the projections.
     """
     if dtype == "float32":
         torch.testing.assert_close(got, want, atol=3e-4, rtol=1e-4)
     else:
         err = (got - want).pow(2).mean(-1).sqrt() / want.std()
         far_off = float((err > 0.12).double().mean())
-        assert far_off <= 0.25 and float(err.median()) < 0.04, \
+        assert int((err > 0.4).sum()) <= max(1, err.numel() // 100) and far_off <= 0.03 and float(err.median()) < 0.04, \
             f"relative error: {far_off:.3f} of the positions over 0.12, worst {float(err.max()):.3f} at {int(err.argmax())}, " \
             f"median {float(err.median()):.3f}"
 
