@@ -218,12 +218,33 @@ moe_linear_rows_kernel(const T* __restrict__ x, long long x_stride, const int* _
     __shared__ float rows_scale[SR];
     T* xs = reinterpret_cast<T*>(raw);                    // [SR][K]
     constexpr int VN = 16 / sizeof(T);
-    int tile = blockIdx.y, e = 0, first = 0, last = 0;
-    for (; e < experts; ++e) {
-        first = offsets[e]; last = offsets[e + 1];
-        const int tiles = (last - first + SR - 1) / SR;
-        if (tile < tiles) break;
-        tile -= tiles;
+    // Which expert's stretch this row tile belongs to (tiles are numbered expert by expert): every warp looks at 32
+    // experts at a time, a lane an expert, and a scan over the lanes' tile counts finds the one; walking the
+    // offsets one dependent load after the other cost the last experts' CTAs some thousand cycles before their first byte.
+    int tile = blockIdx.y, e = experts, first = 0, last = 0;
+    {
+        const int ln = threadIdx.x & 31;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int le = e0 + ln;
+            const int f = le < experts ? offsets[le] : 0, l = le < experts ? offsets[le + 1] : 0;
+            const int tiles = le < experts ? (l - f + SR - 1) / SR : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (ln >= o) incl += v;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, tile < incl);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                e = e0 + src;
+                first = __shfl_sync(0xffffffffu, f, src);
+                last = __shfl_sync(0xffffffffu, l, src);
+                tile -= __shfl_sync(0xffffffffu, incl - tiles, src);
+                break;
+            }
+            tile -= __shfl_sync(0xffffffffu, incl, 31);
+        }
     }
     if (e == experts) return;
     const int row0 = first + tile * SR;
